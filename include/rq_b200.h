@@ -1,0 +1,149 @@
+/*
+ * rq_b200.h -- C ABI of the B200 (sm_100a) W4A4 / W4A4H MUL_MAT path.
+ *
+ * One ggml MUL_MAT node whose weight is of type W4A4 (44) or W4A4H (45): activations f32 [M tokens][K], weight
+ * [N rows][K] in the reference's 144-byte blocks of 256 int4 codes, output f32 [M][N].  The library computes, with
+ * bit-identical results, what the reference's CPU path computes: the online Hadamard rotation of each token
+ * (W4A4H), the per-token grouped asymmetric int4 activation quantizer, the int4 x int4 -> int32 contraction with
+ * the per-group integer fold, and the three-multiply fp32 epilogue.
+ *
+ * Conventions (the same as the reference's GPU entry points, ggml/src/ggml-cuda/rq-w4a4.cuh in
+ * patches/llama.cpp-ruquant.patch:2389-2401, and its demo launcher kernels/rq_scale.cu:11-15): raw device
+ * pointers, the caller's stream, nothing synchronises or allocates on the call path.  Unlike the reference,
+ * which aborts the process on a bad input, every function returns a status (0 = success, negative = rq_status).
+ * Everything first-use (header read, weight re-layout) happens in rq_w4a4_prepare, outside stream capture; the
+ * 144-byte blocks are left untouched (the reference re-packs them in place on first use, rq-w4a4.cu in
+ * patch:2046-2075).
+ */
+#ifndef RQ_B200_H
+#define RQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ggml type ids of the weight (ggml/include/ggml.h in patch:10-11) */
+#define RQ_TYPE_W4A4  44
+#define RQ_TYPE_W4A4H 45
+
+#define RQ_BLOCK_CODES 256   /* QK_W4A4, ggml/src/ggml-common.h in patch:38 */
+#define RQ_BLOCK_BYTES 144   /* sizeof(block_w4a4), patch:44-50 */
+#define RQ_MAX_K       32768 /* the reference admits K <= 256 * 128 blocks (rq-w4a4.cu in patch:1981) */
+#define RQ_MAX_WEIGHTS 3     /* weights sharing one activation in a single call (ggml_cuda_try_fuse, patch:308-329) */
+
+typedef enum rq_status {
+    RQ_OK             =  0,
+    RQ_ERR_ARG        = -1,  /* null pointer, bad type id, bad count */
+    RQ_ERR_SHAPE      = -2,  /* K not a multiple of 256 or above RQ_MAX_K, N or M < 1, misaligned row stride */
+    RQ_ERR_ROTATION   = -3,  /* W4A4H: header rotation length does not divide K or has no H_p x H_m factorisation */
+    RQ_ERR_GROUP      = -4,  /* activation group not 64/128/256, or weight groups of 64 with a group other than 64 */
+    RQ_ERR_WORKSPACE  = -5,  /* workspace or prepack buffer too small or misaligned */
+    RQ_ERR_CUDA       = -6,  /* a CUDA runtime / driver call failed (rq_last_cuda_error has the code) */
+    RQ_ERR_MISMATCH   = -7,  /* weights of one call differ in K, type, rotation length */
+    RQ_ERR_DEVICE     = -8,  /* a kernel gave up on a bounded wait (read by rq_w4a4_device_status) */
+    RQ_ERR_CLIP       = -9,  /* clip not finite or <= 0 */
+    RQ_ERR_LIMIT      = -10  /* a size beyond a stated fixed maximum */
+} rq_status;
+
+/* which kernel-side layouts rq_w4a4_prepare builds */
+#define RQ_PREPACK_DECODE  1   /* int4 stream for the M <= 16 GEMV            (K*N/2 bytes) */
+#define RQ_PREPACK_PREFILL 2   /* int8 operand for the tcgen05 GEMM           (K*N bytes)   */
+#define RQ_PREPACK_ALL     3
+
+/* kernel selection of rq_w4a4_mul_mat */
+#define RQ_PATH_AUTO  0        /* M <= 16: GEMV; else tcgen05 GEMM if prepacked for it, else chunked GEMV */
+#define RQ_PATH_GEMV  1
+#define RQ_PATH_TC    2
+
+/* A prepared weight.  Plain data: filled by rq_w4a4_prepare, read by rq_w4a4_mul_mat; the caller may copy it.
+ * All pointers are device pointers owned by the caller. */
+typedef struct rq_weight_desc {
+    int32_t  type;          /* RQ_TYPE_W4A4 / RQ_TYPE_W4A4H */
+    int32_t  layouts;       /* RQ_PREPACK_* bits present in `prepack` */
+    int64_t  K, N;
+    int32_t  n_rot;         /* W4A4H: Hadamard length from block 0's pad[0]; 0 for W4A4 */
+    int32_t  had_p, had_m;  /* n_rot = had_p * had_m, had_m a power of two */
+    int32_t  wk_mode;       /* 0: every weight multiplier is 1; 1: multipliers present (per block or per 64 inputs) */
+    int32_t  wg64;          /* block 0's header selects weight groups of 64 (needs activation groups of 64) */
+    float    header_clip;   /* block 0's pad[1] as a float; 0 = unset */
+    const void * blocks;    /* the 144-byte blocks as given */
+    void *   prepack;       /* base of the prepack buffer */
+    uint64_t off_sw;        /* f32  [N]        row units s_w */
+    uint64_t off_w4;        /* u8   [N][K/2]   decode stream (if RQ_PREPACK_DECODE) */
+    uint64_t off_w8;        /* i8   [N][K]     prefill operand (if RQ_PREPACK_PREFILL) */
+    uint64_t off_wk;        /* i8   [N][K/64]  weight multipliers (if wk_mode) */
+    uint64_t tmap_w8[16];   /* CUtensorMap of the prefill operand (128 bytes, 64-byte aligned copy is made at launch) */
+} rq_weight_desc;
+
+/* Admitted shapes.  Mirrors ggml_cuda_rq_w4a4_supported (rq-w4a4.cu in patch:1977-1994): K a multiple of 256 and
+ * <= 32768, x rows 16-byte aligned, W4A4H needs a factorable K -- but any N >= 1 and any M >= 1 are accepted
+ * (the reference needs N a multiple of 32).  Returns 1 if supported, 0 if not. */
+int rq_w4a4_supported(int type, int64_t K, int64_t N, int64_t M, int64_t ldx_bytes);
+
+/* The reference's factorisation of a Hadamard length (ggml_rq_hadamard_factor, ggml/src/ggml-quants.c in
+ * patch:2419-2430).  Returns 1 and fills p, m, or 0. */
+int rq_hadamard_factor(int64_t n, int * p, int * m);
+
+/* Resolution of the run-time switches exactly as the reference does it, environment included:
+ * clip = RQ_ACT_CLIP / RQ_ACT_CLIP_H if > 0, else the tensor's header clip if > 0, else 1
+ * (ggml_rq_act_clip_for, patch:2590-2600); group = RQ_ACT_GROUP if 128 or 256, else 64 (ggml_rq_act_group,
+ * patch:2623-2631). */
+float rq_w4a4_resolve_clip(const rq_weight_desc * w);
+int   rq_w4a4_act_group(void);
+
+/* Bytes of the caller-owned prepack buffer for one weight. */
+size_t rq_w4a4_prepack_bytes(int type, int64_t K, int64_t N, int layouts);
+
+/* First use of a weight; NOT capture-safe (copies block 0's header to the host and synchronises `stream`, as
+ * rq_info does in patch:2027-2043).  Reads clip, rotation length and weight-group mode, validates them, builds the
+ * kernel-side layouts in `prepack_dev` (256-byte aligned, rq_w4a4_prepack_bytes large).  The blocks stay valid and
+ * untouched. */
+int rq_w4a4_prepare(const void * w_blocks_dev, int type, int64_t K, int64_t N, void * prepack_dev, size_t prepack_bytes,
+                    int layouts, rq_weight_desc * out_desc, void * stream);
+
+/* Bytes of the per-call workspace (quantized activations and a status word) for M tokens of width K. */
+size_t rq_w4a4_workspace_bytes(int64_t K, int64_t M);
+
+/* The MUL_MAT node.  Capture-safe: only enqueues on `stream`.  y[i][t*ldy[i] + n] for n_w (1..3) weights that
+ * share the activation x (f32, row stride ldx floats, rows 16-byte aligned): rotate (W4A4H) -> quantize -> GEMV
+ * or tcgen05 GEMM with the per-group fold -> epilogue.  clip and act_group are the resolved values (see
+ * rq_w4a4_resolve_clip / rq_w4a4_act_group).  Replaces ggml_cuda_mul_mat_rq_w4a4 and ggml_cuda_mul_mat_rq_w4a4_fused
+ * (rq-w4a4.cu in patch:2341-2380). */
+int rq_w4a4_mul_mat(const rq_weight_desc * const * w, int n_w, const float * x_dev, int64_t ldx, int64_t M,
+                    float * const * y_dev, const int64_t * ldy, float clip, int act_group, int path,
+                    void * workspace_dev, size_t workspace_bytes, void * stream);
+
+/* The GEMM / GEMV stage alone on an activation that rq_w4a4_quantize already left in `workspace_dev` (the
+ * explicit form of the reference's activation cache, rq-w4a4.cu in patch:1996-2023). */
+int rq_w4a4_mul_mat_quantized(const rq_weight_desc * w, int64_t M, float * y_dev, int64_t ldy, int act_group, int path,
+                              void * workspace_dev, size_t workspace_bytes, void * stream);
+
+/* Stage entry points (also used by the parity tests).
+ * rq_w4a4_rotate: out[t][:] = x[t][:] * diag(H, H, ...) with H = (H_p kron H_m)/sqrt(n_rot)
+ *   (ggml_rq_hadamard per block of n_rot, patch:2450-2485, 2697-2699).
+ * rq_w4a4_quantize: rotate (n_rot > 0) and quantize M tokens into the workspace
+ *   (quantize_row_a4_clip / quantize_row_a4h_clip_n, patch:2639-2679, 2720-2736). */
+int rq_w4a4_rotate(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float * out_dev, int64_t ldo,
+                   void * stream);
+int rq_w4a4_quantize(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float clip, int act_group,
+                     void * workspace_dev, size_t workspace_bytes, void * stream);
+
+/* Where the quantized activation sits in the workspace: a8 = int8 [M][K] holding 8*(q - z_g); msh = int32
+ * [M][K/act_group] holding m_g << 21; u = f32 [M] token units. */
+int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off_a8, uint64_t * off_msh, uint64_t * off_u,
+                             uint64_t * off_status);
+
+/* Synchronises `stream` and returns RQ_OK or RQ_ERR_DEVICE if a kernel of an earlier call on this workspace gave
+ * up on a bounded wait.  Not capture-safe. */
+int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream);
+
+const char * rq_status_string(int status);
+int rq_last_cuda_error(void);   /* cudaError_t of the last failed runtime call on this thread */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RQ_B200_H */

@@ -1,0 +1,223 @@
+"""ruquant_b200 -- B200 (sm_100a) W4A4 / W4A4H MUL_MAT behind ruquant's ggml operator surface.
+
+The product is the C-ABI library `librq_b200.so` (declared in include/rq_b200.h, built in-tree by
+`python -m ruquant_b200.build`).  This package is its Python host side: ctypes bindings plus thin helpers that use
+torch only for device memory and streams.  There is no CPU or PyTorch fallback: importing the bindings without the
+built library raises, and every compute call goes through the library's CUDA kernels.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "librq_b200.so")
+
+TYPE_W4A4, TYPE_W4A4H = 44, 45
+BLOCK_CODES, BLOCK_BYTES = 256, 144
+PREPACK_DECODE, PREPACK_PREFILL, PREPACK_ALL = 1, 2, 3
+PATH_AUTO, PATH_GEMV, PATH_TC = 0, 1, 2
+
+EXPORTS = [
+    "rq_w4a4_supported", "rq_hadamard_factor", "rq_w4a4_resolve_clip", "rq_w4a4_act_group", "rq_w4a4_prepack_bytes",
+    "rq_w4a4_prepare", "rq_w4a4_workspace_bytes", "rq_w4a4_mul_mat", "rq_w4a4_mul_mat_quantized", "rq_w4a4_rotate",
+    "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
+]
+
+
+class RqError(RuntimeError):
+    def __init__(self, status, what):
+        self.status = status
+        super().__init__("%s: %s (status %d)" % (what, lib().rq_status_string(status).decode(), status))
+
+
+class WeightDesc(ctypes.Structure):
+    """rq_weight_desc of include/rq_b200.h."""
+    _fields_ = [
+        ("type", ctypes.c_int32), ("layouts", ctypes.c_int32), ("K", ctypes.c_int64), ("N", ctypes.c_int64),
+        ("n_rot", ctypes.c_int32), ("had_p", ctypes.c_int32), ("had_m", ctypes.c_int32), ("wk_mode", ctypes.c_int32),
+        ("wg64", ctypes.c_int32), ("header_clip", ctypes.c_float), ("blocks", ctypes.c_void_p), ("prepack", ctypes.c_void_p),
+        ("off_sw", ctypes.c_uint64), ("off_w4", ctypes.c_uint64), ("off_w8", ctypes.c_uint64), ("off_wk", ctypes.c_uint64),
+        ("tmap_w8", ctypes.c_uint64 * 16),
+    ]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded C-ABI library.  Raises if it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("librq_b200.so is not built (run `python -m ruquant_b200.build`); "
+                              "ruquant_b200 has no CPU or PyTorch fallback")
+        L = ctypes.CDLL(LIB_PATH)
+        i64, i32, vp, f32, sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_size_t
+        pd = ctypes.POINTER(WeightDesc)
+        L.rq_w4a4_supported.argtypes = [i32, i64, i64, i64, i64]
+        L.rq_hadamard_factor.argtypes = [i64, ctypes.POINTER(i32), ctypes.POINTER(i32)]
+        L.rq_w4a4_resolve_clip.argtypes = [pd]
+        L.rq_w4a4_resolve_clip.restype = f32
+        L.rq_w4a4_act_group.argtypes = []
+        L.rq_w4a4_prepack_bytes.argtypes = [i32, i64, i64, i32]
+        L.rq_w4a4_prepack_bytes.restype = sz
+        L.rq_w4a4_prepare.argtypes = [vp, i32, i64, i64, vp, sz, i32, pd, vp]
+        L.rq_w4a4_workspace_bytes.argtypes = [i64, i64]
+        L.rq_w4a4_workspace_bytes.restype = sz
+        L.rq_w4a4_mul_mat.argtypes = [ctypes.POINTER(pd), i32, vp, i64, i64, ctypes.POINTER(vp), ctypes.POINTER(i64), f32, i32,
+                                      i32, vp, sz, vp]
+        L.rq_w4a4_mul_mat_quantized.argtypes = [pd, i64, vp, i64, i32, i32, vp, sz, vp]
+        L.rq_w4a4_rotate.argtypes = [vp, i64, i64, i64, i64, vp, i64, vp]
+        L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, vp, sz, vp]
+        u64p = ctypes.POINTER(ctypes.c_uint64)
+        L.rq_w4a4_workspace_layout.argtypes = [i64, i64, i32, u64p, u64p, u64p, u64p]
+        L.rq_w4a4_device_status.argtypes = [vp, i64, i64, vp]
+        L.rq_status_string.argtypes = [i32]
+        L.rq_status_string.restype = ctypes.c_char_p
+        L.rq_last_cuda_error.argtypes = []
+        _lib = L
+    return _lib
+
+
+def _check(status, what):
+    if status != 0:
+        raise RqError(status, what)
+
+
+def hadamard_factor(n):
+    p, m = ctypes.c_int(0), ctypes.c_int(0)
+    return (p.value, m.value) if lib().rq_hadamard_factor(n, ctypes.byref(p), ctypes.byref(m)) else None
+
+
+def supported(type_, K, N, M, ldx_bytes=None):
+    return bool(lib().rq_w4a4_supported(type_, K, N, M, ldx_bytes if ldx_bytes is not None else 4 * K))
+
+
+def _stream_ptr(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+class Weight:
+    """A W4A4 / W4A4H weight prepared for the kernels.
+
+    blocks: torch.uint8 CUDA tensor holding N rows of K/256 144-byte blocks (the ggml tensor's data).  It is only
+    read; the kernel-side layouts live in a separate prepack tensor owned by this object."""
+
+    def __init__(self, blocks, type_, K, N=None, layouts=PREPACK_ALL, stream=None):
+        import torch
+        if not blocks.is_cuda or blocks.dtype != torch.uint8 or not blocks.is_contiguous():
+            raise ValueError("blocks must be a contiguous uint8 CUDA tensor")
+        row_bytes = K // BLOCK_CODES * BLOCK_BYTES
+        if N is None:
+            N = blocks.numel() // row_bytes
+        if blocks.numel() != N * row_bytes:
+            raise ValueError("blocks has %d bytes, expected %d" % (blocks.numel(), N * row_bytes))
+        self.blocks, self.type, self.K, self.N = blocks, type_, K, N
+        nbytes = lib().rq_w4a4_prepack_bytes(type_, K, N, layouts)
+        if nbytes == 0:
+            raise RqError(-2, "rq_w4a4_prepack_bytes")
+        self.prepack = torch.empty(nbytes, dtype=torch.uint8, device=blocks.device)
+        self.desc = WeightDesc()
+        with torch.cuda.device(blocks.device):
+            _check(lib().rq_w4a4_prepare(blocks.data_ptr(), type_, K, N, self.prepack.data_ptr(), nbytes, layouts,
+                                         ctypes.byref(self.desc), _stream_ptr(stream)), "rq_w4a4_prepare")
+
+    @property
+    def n_rot(self):
+        return self.desc.n_rot
+
+    def clip(self):
+        """The activation clip the reference would use: environment, else header, else 1."""
+        return lib().rq_w4a4_resolve_clip(ctypes.byref(self.desc))
+
+
+def workspace_bytes(K, M):
+    return lib().rq_w4a4_workspace_bytes(K, M)
+
+
+def new_workspace(K, M, device="cuda"):
+    import torch
+    return torch.empty(workspace_bytes(K, M), dtype=torch.uint8, device=device)
+
+
+def workspace_views(ws, K, M, group):
+    """(a8 int8 [M, K], msh int32 [M, K/group], u f32 [M]) views into a workspace tensor."""
+    import torch
+    o = [ctypes.c_uint64(0) for _ in range(4)]
+    _check(lib().rq_w4a4_workspace_layout(K, M, group, *[ctypes.byref(v) for v in o]), "rq_w4a4_workspace_layout")
+    a8 = ws[o[0].value:o[0].value + M * K].view(torch.int8).view(M, K)
+    ng = K // group
+    msh = ws[o[1].value:o[1].value + M * ng * 4].view(torch.int32).view(M, ng)
+    u = ws[o[2].value:o[2].value + M * 4].view(torch.float32)
+    return a8, msh, u
+
+
+def mul_mat(weights, x, out=None, clip=None, act_group=None, path=PATH_AUTO, workspace=None, stream=None):
+    """The MUL_MAT node: y[i] = x @ W[i]^T for 1..3 prepared weights sharing the f32 activation x [M, K].
+    Returns one tensor [M, N] (single weight) or a list.  Only enqueues on the stream."""
+    import torch
+    single = isinstance(weights, Weight)
+    ws_list = [weights] if single else list(weights)
+    if x.dtype != torch.float32 or not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be a 2-D f32 CUDA tensor with unit inner stride")
+    M, K = x.shape
+    n_w = len(ws_list)
+    if out is None:
+        outs = [torch.empty((M, w.N), dtype=torch.float32, device=x.device) for w in ws_list]
+    else:
+        outs = [out] if single else list(out)
+    if clip is None:
+        clip = ws_list[0].clip()
+    if act_group is None:
+        act_group = lib().rq_w4a4_act_group()
+    if workspace is None:
+        workspace = new_workspace(K, M, x.device)
+    pd = ctypes.POINTER(WeightDesc)
+    descs = (pd * n_w)(*[ctypes.pointer(w.desc) for w in ws_list])
+    ys = (ctypes.c_void_p * n_w)(*[o.data_ptr() for o in outs])
+    ldy = (ctypes.c_int64 * n_w)(*[o.stride(0) for o in outs])
+    with torch.cuda.device(x.device):
+        _check(lib().rq_w4a4_mul_mat(descs, n_w, x.data_ptr(), x.stride(0), M, ys, ldy, clip, act_group, path,
+                                     workspace.data_ptr(), workspace.numel(), _stream_ptr(stream)), "rq_w4a4_mul_mat")
+    return outs[0] if single else outs
+
+
+def rotate(x, n_rot, stream=None):
+    """Rows of x (f32 CUDA [M, K]) times diag(H, H, ...), H of length n_rot: the online Hadamard alone."""
+    import torch
+    M, K = x.shape
+    out = torch.empty((M, K), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib().rq_w4a4_rotate(x.data_ptr(), x.stride(0), M, K, n_rot, out.data_ptr(), out.stride(0),
+                                    _stream_ptr(stream)), "rq_w4a4_rotate")
+    return out
+
+
+def quantize(x, n_rot, clip, group=64, workspace=None, stream=None):
+    """Rotate (n_rot > 0) and quantize; returns (workspace, a8, msh, u)."""
+    M, K = x.shape
+    if workspace is None:
+        workspace = new_workspace(K, M, x.device)
+    import torch
+    with torch.cuda.device(x.device):
+        _check(lib().rq_w4a4_quantize(x.data_ptr(), x.stride(0), M, K, n_rot, clip, group, workspace.data_ptr(),
+                                      workspace.numel(), _stream_ptr(stream)), "rq_w4a4_quantize")
+    return (workspace,) + workspace_views(workspace, K, M, group)
+
+
+def mul_mat_quantized(weight, M, workspace, out=None, act_group=64, path=PATH_AUTO, stream=None):
+    """The contraction stage alone, on an activation already quantized into `workspace`."""
+    import torch
+    if out is None:
+        out = torch.empty((M, weight.N), dtype=torch.float32, device=workspace.device)
+    with torch.cuda.device(workspace.device):
+        _check(lib().rq_w4a4_mul_mat_quantized(ctypes.byref(weight.desc), M, out.data_ptr(), out.stride(0), act_group, path,
+                                               workspace.data_ptr(), workspace.numel(), _stream_ptr(stream)),
+               "rq_w4a4_mul_mat_quantized")
+    return out
+
+
+def device_status(workspace, K, M, stream=None):
+    """Synchronises and raises if a kernel of the last call on this workspace gave up on a bounded wait."""
+    _check(lib().rq_w4a4_device_status(workspace.data_ptr(), K, M, _stream_ptr(stream)), "rq_w4a4_device_status")

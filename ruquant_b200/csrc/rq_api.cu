@@ -1,0 +1,293 @@
+// C ABI of the library (declared in include/rq_b200.h): argument checks, header decoding, layout bookkeeping and
+// kernel dispatch.  Mirrors the host logic of the reference's ggml/src/ggml-cuda/rq-w4a4.cu
+// (patches/llama.cpp-ruquant.patch:1977-2043 supported / first-use header read, 2145-2338 dispatch) with status
+// codes in place of aborts and with every first-use step moved into rq_w4a4_prepare.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "rq_common.cuh"
+
+static thread_local int g_last_cuda = 0;
+
+#define RQ_CUDA(call)                                             \
+    do {                                                          \
+        const cudaError_t e_ = (call);                            \
+        if (e_ != cudaSuccess) { g_last_cuda = (int) e_; return RQ_ERR_CUDA; } \
+    } while (0)
+
+extern "C" __attribute__((visibility("default"))) int rq_last_cuda_error(void) { return g_last_cuda; }
+
+extern "C" __attribute__((visibility("default"))) const char * rq_status_string(int status) {
+    switch (status) {
+        case RQ_OK:            return "ok";
+        case RQ_ERR_ARG:       return "bad argument (null pointer, type id or count)";
+        case RQ_ERR_SHAPE:     return "unsupported shape (K must be a multiple of 256 and <= 32768; rows 16-byte aligned)";
+        case RQ_ERR_ROTATION:  return "W4A4H: Hadamard length does not divide K or does not factor (ruquant convert --rot-blocks)";
+        case RQ_ERR_GROUP:     return "activation group must be 64, 128 or 256 (64 with weight groups of 64)";
+        case RQ_ERR_WORKSPACE: return "workspace or prepack buffer too small or misaligned";
+        case RQ_ERR_CUDA:      return "CUDA call failed (see rq_last_cuda_error)";
+        case RQ_ERR_MISMATCH:  return "weights of one call differ in K, type or rotation";
+        case RQ_ERR_DEVICE:    return "a kernel gave up on a bounded wait";
+        case RQ_ERR_CLIP:      return "clip must be finite and > 0";
+        case RQ_ERR_LIMIT:     return "size beyond a fixed maximum";
+        default:               return "unknown status";
+    }
+}
+
+static bool rq_is_prime(int q) {
+    if (q < 2) return false;
+    for (int d = 2; d * d <= q; ++d) if (q % d == 0) return false;
+    return true;
+}
+
+// ggml_rq_hadamard_factor, ggml/src/ggml-quants.c in patch:2419-2430
+extern "C" __attribute__((visibility("default"))) int rq_hadamard_factor(int64_t n, int * p, int * m) {
+    for (int c = 1; c <= 128 && c <= n; ++c) {
+        if (c > 1 && !(c % 4 == 0 && rq_is_prime(c - 1) && (c - 1) % 4 == 3)) continue;
+        if (n % c != 0) continue;
+        const int64_t rest = n / c;
+        if (rest & (rest - 1)) continue;
+        if (p) *p = c;
+        if (m) *m = (int) rest;
+        return 1;
+    }
+    return 0;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_supported(int type, int64_t K, int64_t N, int64_t M, int64_t ldx_bytes) {
+    if (type != RQ_TYPE_W4A4 && type != RQ_TYPE_W4A4H) return 0;
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || K > RQ_MAX_K || N < 1 || M < 1) return 0;
+    if (ldx_bytes < K * 4 || ldx_bytes % 16 != 0) return 0;
+    if (type == RQ_TYPE_W4A4H && !rq_hadamard_factor(K, nullptr, nullptr)) return 0;
+    return 1;
+}
+
+// ggml_rq_act_clip_for, patch:2590-2600: RQ_ACT_CLIP (and RQ_ACT_CLIP_H for rotated inputs, defaulting to
+// RQ_ACT_CLIP) win over the tensor's own clip, which wins over 1
+extern "C" __attribute__((visibility("default"))) float rq_w4a4_resolve_clip(const rq_weight_desc * w) {
+    static float env[2] = { -2.0f, -2.0f };
+    if (env[0] == -2.0f) {
+        const char * e = getenv("RQ_ACT_CLIP");
+        const char * eh = getenv("RQ_ACT_CLIP_H");
+        const float e0 = e ? (float) atof(e) : -1.0f;
+        env[1] = eh ? (float) atof(eh) : e0;
+        env[0] = e0;
+    }
+    const bool had = w != nullptr && w->type == RQ_TYPE_W4A4H;
+    const float e = env[had ? 1 : 0];
+    const float t = w != nullptr ? w->header_clip : 0.0f;
+    return e > 0.0f ? e : t > 0.0f ? t : 1.0f;
+}
+
+// ggml_rq_act_group, patch:2623-2631
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_act_group(void) {
+    static int g = 0;
+    if (g == 0) {
+        const char * e = getenv("RQ_ACT_GROUP");
+        const int v = e ? atoi(e) : 64;
+        g = (v == 128 || v == 256) ? v : 64;
+    }
+    return g;
+}
+
+struct rq_pp_layout {
+    uint64_t off_sw, off_w4, off_w8, off_wk, bytes;
+};
+static rq_pp_layout rq_pp(int64_t K, int64_t N, int layouts) {
+    rq_pp_layout l;
+    l.off_sw = 0;
+    l.off_wk = rq_align256((uint64_t) N * 4);
+    l.off_w4 = l.off_wk + rq_align256((uint64_t) N * (K / 64));
+    l.off_w8 = l.off_w4 + ((layouts & RQ_PREPACK_DECODE) ? rq_align256((uint64_t) N * K / 2) : 0);
+    l.bytes = l.off_w8 + ((layouts & RQ_PREPACK_PREFILL) ? rq_align256((uint64_t) N * K) : 0);
+    return l;
+}
+
+extern "C" __attribute__((visibility("default"))) size_t rq_w4a4_prepack_bytes(int type, int64_t K, int64_t N, int layouts) {
+    if ((type != RQ_TYPE_W4A4 && type != RQ_TYPE_W4A4H) || K <= 0 || K % RQ_BLOCK_CODES != 0 || N < 1) return 0;
+    return (size_t) rq_pp(K, N, layouts & RQ_PREPACK_ALL).bytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_prepare(const void * w_blocks_dev, int type, int64_t K, int64_t N, void * prepack_dev,
+                               size_t prepack_bytes, int layouts, rq_weight_desc * out, void * stream_) {
+    cudaStream_t stream = (cudaStream_t) stream_;
+    if (w_blocks_dev == nullptr || prepack_dev == nullptr || out == nullptr) return RQ_ERR_ARG;
+    if (type != RQ_TYPE_W4A4 && type != RQ_TYPE_W4A4H) return RQ_ERR_ARG;
+    layouts &= RQ_PREPACK_ALL;
+    if (layouts == 0) return RQ_ERR_ARG;
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || K > RQ_MAX_K || N < 1) return RQ_ERR_SHAPE;
+    const rq_pp_layout l = rq_pp(K, N, layouts);
+    if (prepack_bytes < l.bytes || (reinterpret_cast<uintptr_t>(prepack_dev) & 255) != 0) return RQ_ERR_WORKSPACE;
+
+    // block 0 of row 0 carries the tensor's switches (ggml_rq_tensor_clip / ggml_rq_tensor_rot, patch:2602-2610;
+    // rq_info, patch:2027-2043): sum -> weight-group mode, pad[0] -> Hadamard length, pad[1] -> clip
+    rq_block hdr;
+    uint8_t * pp = static_cast<uint8_t *>(prepack_dev);
+    int32_t * flag_dev = reinterpret_cast<int32_t *>(pp + l.off_wk);   // scratch until the pack kernel overwrites it
+    int32_t flag = 0;
+    RQ_CUDA(cudaMemcpyAsync(&hdr, w_blocks_dev, 16, cudaMemcpyDeviceToHost, stream));
+    RQ_CUDA(cudaMemsetAsync(flag_dev, 0, 4, stream));
+    RQ_CUDA(rq_launch_scan_wk(static_cast<const rq_block *>(w_blocks_dev), N * (K / RQ_BLOCK_CODES), flag_dev, stream));
+    RQ_CUDA(cudaMemcpyAsync(&flag, flag_dev, 4, cudaMemcpyDeviceToHost, stream));
+    RQ_CUDA(cudaStreamSynchronize(stream));
+
+    memset(out, 0, sizeof(*out));
+    out->type = type;
+    out->layouts = layouts;
+    out->K = K;
+    out->N = N;
+    memcpy(&out->header_clip, &hdr.pad[1], 4);
+    if (!(out->header_clip == out->header_clip) || isinf(out->header_clip)) return RQ_ERR_CLIP;
+    out->wg64 = (((uint32_t) hdr.sum) >> 29) == 3u ? 1 : 0;
+    out->wk_mode = flag ? 1 : 0;
+    out->had_p = 1;
+    if (type == RQ_TYPE_W4A4H) {
+        const int32_t n = hdr.pad[0];   // ggml_rq_rot_check, patch:2612-2620
+        int p = 0, m = 0;
+        if (n <= 0 || K % n != 0 || !rq_hadamard_factor(n, &p, &m)) return RQ_ERR_ROTATION;
+        out->n_rot = n;
+        out->had_p = p;
+        out->had_m = m;
+    }
+    out->blocks = w_blocks_dev;
+    out->prepack = prepack_dev;
+    out->off_sw = l.off_sw;
+    out->off_w4 = l.off_w4;
+    out->off_w8 = l.off_w8;
+    out->off_wk = l.off_wk;
+
+    RQ_CUDA(rq_launch_prepack(static_cast<const rq_block *>(w_blocks_dev), K, N, reinterpret_cast<float *>(pp + l.off_sw),
+                              (layouts & RQ_PREPACK_DECODE) ? pp + l.off_w4 : nullptr,
+                              (layouts & RQ_PREPACK_PREFILL) ? reinterpret_cast<int8_t *>(pp + l.off_w8) : nullptr,
+                              reinterpret_cast<int8_t *>(pp + l.off_wk), out->wk_mode, stream));
+    if (layouts & RQ_PREPACK_PREFILL) {
+        if (rq_encode_tmap_i8(out->tmap_w8, pp + l.off_w8, K, N, 256) != 0) return RQ_ERR_CUDA;
+    }
+    RQ_CUDA(cudaStreamSynchronize(stream));
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) size_t rq_w4a4_workspace_bytes(int64_t K, int64_t M) {
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || M < 1) return 0;
+    return (size_t) rq_ws(K, M).bytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off_a8, uint64_t * off_msh,
+                                        uint64_t * off_u, uint64_t * off_status) {
+    (void) act_group;
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || M < 1) return RQ_ERR_SHAPE;
+    const rq_ws_layout l = rq_ws(K, M);
+    if (off_a8) *off_a8 = l.off_a8;
+    if (off_msh) *off_msh = l.off_msh;
+    if (off_u) *off_u = l.off_u;
+    if (off_status) *off_status = l.off_status;
+    return RQ_OK;
+}
+
+static int rq_check_x(const float * x, int64_t ldx, int64_t M, int64_t K) {
+    if (x == nullptr) return RQ_ERR_ARG;
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || K > RQ_MAX_K || M < 1) return RQ_ERR_SHAPE;
+    if (ldx < K || (ldx * 4) % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return RQ_ERR_SHAPE;
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_rotate(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float * out_dev,
+                              int64_t ldo, void * stream) {
+    int rc = rq_check_x(x_dev, ldx, M, K);
+    if (rc != RQ_OK) return rc;
+    rc = rq_check_x(out_dev, ldo, M, K);
+    if (rc != RQ_OK) return rc;
+    int p = 0, m = 0;
+    if (n_rot <= 0 || K % n_rot != 0 || !rq_hadamard_factor(n_rot, &p, &m)) return RQ_ERR_ROTATION;
+    const float scale = 1.0f / sqrtf((float) n_rot);
+    RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, 1.0f, 64, nullptr, nullptr, nullptr, out_dev, ldo,
+                          (cudaStream_t) stream));
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float clip,
+                                int act_group, void * workspace_dev, size_t workspace_bytes, void * stream) {
+    int rc = rq_check_x(x_dev, ldx, M, K);
+    if (rc != RQ_OK) return rc;
+    if (act_group != 64 && act_group != 128 && act_group != 256) return RQ_ERR_GROUP;
+    if (!(clip > 0.0f) || isinf(clip)) return RQ_ERR_CLIP;
+    const rq_ws_layout l = rq_ws(K, M);
+    if (workspace_dev == nullptr || workspace_bytes < l.bytes || (reinterpret_cast<uintptr_t>(workspace_dev) & 255) != 0)
+        return RQ_ERR_WORKSPACE;
+    int p = 1, m = 0;
+    float scale = 1.0f;
+    if (n_rot > 0) {
+        if (K % n_rot != 0 || !rq_hadamard_factor(n_rot, &p, &m)) return RQ_ERR_ROTATION;
+        scale = 1.0f / sqrtf((float) n_rot);
+    } else if (n_rot < 0) {
+        return RQ_ERR_ROTATION;
+    }
+    uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
+    RQ_CUDA(cudaMemsetAsync(ws + l.off_status, 0, 4, (cudaStream_t) stream));
+    RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, clip, act_group, reinterpret_cast<int8_t *>(ws + l.off_a8),
+                          reinterpret_cast<int32_t *>(ws + l.off_msh), reinterpret_cast<float *>(ws + l.off_u), nullptr, 0,
+                          (cudaStream_t) stream));
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(const rq_weight_desc * w, int64_t M, float * y_dev, int64_t ldy, int act_group,
+                                         int path, void * workspace_dev, size_t workspace_bytes, void * stream_) {
+    cudaStream_t stream = (cudaStream_t) stream_;
+    if (w == nullptr || y_dev == nullptr || w->prepack == nullptr) return RQ_ERR_ARG;
+    if (M < 1 || ldy < w->N) return RQ_ERR_SHAPE;
+    if (act_group != 64 && act_group != 128 && act_group != 256) return RQ_ERR_GROUP;
+    if (w->wg64 && act_group != 64) return RQ_ERR_GROUP;   // ggml_vec_dot_w4a4_a4's assert, patch:171
+    const rq_ws_layout l = rq_ws(w->K, M);
+    if (workspace_dev == nullptr || workspace_bytes < l.bytes) return RQ_ERR_WORKSPACE;
+    const uint8_t * ws = static_cast<const uint8_t *>(workspace_dev);
+    const uint8_t * pp = static_cast<const uint8_t *>(w->prepack);
+    const int8_t * a8 = reinterpret_cast<const int8_t *>(ws + l.off_a8);
+    const int32_t * msh = reinterpret_cast<const int32_t *>(ws + l.off_msh);
+    const float * u = reinterpret_cast<const float *>(ws + l.off_u);
+    const float * sw = reinterpret_cast<const float *>(pp + w->off_sw);
+    const bool has_dec = (w->layouts & RQ_PREPACK_DECODE) != 0, has_pre = (w->layouts & RQ_PREPACK_PREFILL) != 0;
+    bool tc;
+    if (path == RQ_PATH_GEMV) { if (!has_dec) return RQ_ERR_ARG; tc = false; }
+    else if (path == RQ_PATH_TC) { if (!has_pre) return RQ_ERR_ARG; tc = true; }
+    else if (path == RQ_PATH_AUTO) tc = has_pre && (M > 16 || !has_dec);
+    else return RQ_ERR_ARG;
+    if (tc) {
+        int32_t * status = reinterpret_cast<int32_t *>(const_cast<uint8_t *>(ws) + l.off_status);
+        RQ_CUDA(rq_launch_gemm_tc(w->tmap_w8, sw, w->wk_mode, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
+    } else {
+        const int8_t * wk = w->wk_mode ? reinterpret_cast<const int8_t *>(pp + w->off_wk) : nullptr;
+        RQ_CUDA(rq_launch_gemv(pp + w->off_w4, sw, wk, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, stream));
+    }
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat(const rq_weight_desc * const * w, int n_w, const float * x_dev, int64_t ldx, int64_t M,
+                               float * const * y_dev, const int64_t * ldy, float clip, int act_group, int path,
+                               void * workspace_dev, size_t workspace_bytes, void * stream) {
+    if (w == nullptr || y_dev == nullptr || ldy == nullptr || n_w < 1 || n_w > RQ_MAX_WEIGHTS) return RQ_ERR_ARG;
+    for (int i = 0; i < n_w; ++i) {
+        if (w[i] == nullptr || y_dev[i] == nullptr) return RQ_ERR_ARG;
+        // one activation serves all: same input width, type and rotation (ggml_cuda_rq_w4a4_can_fuse, patch:2394-2397)
+        if (w[i]->K != w[0]->K || w[i]->type != w[0]->type || w[i]->n_rot != w[0]->n_rot) return RQ_ERR_MISMATCH;
+    }
+    int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group,
+                              workspace_dev, workspace_bytes, stream);
+    if (rc != RQ_OK) return rc;
+    for (int i = 0; i < n_w; ++i) {
+        rc = rq_w4a4_mul_mat_quantized(w[i], M, y_dev[i], ldy[i], act_group, path, workspace_dev, workspace_bytes, stream);
+        if (rc != RQ_OK) return rc;
+    }
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream) {
+    if (workspace_dev == nullptr) return RQ_ERR_ARG;
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || M < 1) return RQ_ERR_SHAPE;
+    const rq_ws_layout l = rq_ws(K, M);
+    int32_t st = 0;
+    RQ_CUDA(cudaMemcpyAsync(&st, static_cast<uint8_t *>(workspace_dev) + l.off_status, 4, cudaMemcpyDeviceToHost,
+                            (cudaStream_t) stream));
+    RQ_CUDA(cudaStreamSynchronize((cudaStream_t) stream));
+    return st ? RQ_ERR_DEVICE : RQ_OK;
+}

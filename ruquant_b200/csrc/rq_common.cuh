@@ -1,0 +1,64 @@
+// Shared declarations of the sm_100a W4A4 / W4A4H MUL_MAT library (internal; the public face is include/rq_b200.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/rq_b200.h"
+
+// 144-byte block of 256 int4 codes: element 8w+j in bits [4j+3:4j] of qs[w], two's complement
+// (block_w4a4, ggml/src/ggml-common.h in patches/llama.cpp-ruquant.patch:26-50 of the reference).
+struct rq_block {
+    float    d;        // weights: the row's unit s_w
+    int32_t  sum;      // weights: legacy code sum, or 1<<30 | k_b, or 3<<29 | k0 | k1<<4 | k2<<8 | k3<<12
+    int32_t  pad[2];   // weights: pad[0] = row length (W4A4) / Hadamard length (W4A4H), pad[1] = clip as float bits
+    uint32_t qs[32];
+};
+static_assert(sizeof(rq_block) == RQ_BLOCK_BYTES, "block layout");
+
+// weight multiplier of the g-th run of 64 inputs of a block (RQ_W_MULT_G, patch:40-43)
+__host__ __device__ inline int rq_wmult(int32_t sum, int g) {
+    const uint32_t s = (uint32_t) sum;
+    if ((s >> 29) == 3u) return (int) ((s >> (4 * g)) & 0xF);
+    if ((s >> 30) == 1u) return (int) (s & 0xF);
+    return 1;
+}
+
+// The activation multiplier m_g (1..255) is stored pre-shifted so that one signed high multiply folds a group:
+// the contraction delivers D = 128 * S (weights as 16*c, activations as 8*(q-z)), and
+// mulhi(D, m << 21) = floor(128*S*m*2^21 / 2^32) = (m*S) >> 4, the reference's arithmetic shift
+// (RQ_TERM_SHIFT, patch:39 and ggml_vec_dot_w4a4_a4, patch:173).
+#define RQ_MSH_SHIFT 21
+#define RQ_ACT_SCALE 8     // activations are stored as 8*(q - z), |.| <= 120
+#define RQ_W_SCALE   16    // weights with multiplier 1 are stored as 16*c, in [-128, 112]
+
+// Workspace of one call: [a8 int8 M*K][msh int32 M*(K/64)][u f32 M][status int32 x 64], each part 256-byte aligned.
+struct rq_ws_layout {
+    uint64_t off_a8, off_msh, off_u, off_status, bytes;
+};
+static inline uint64_t rq_align256(uint64_t v) { return (v + 255) & ~(uint64_t) 255; }
+static inline rq_ws_layout rq_ws(int64_t K, int64_t M) {
+    rq_ws_layout l;
+    l.off_a8 = 0;
+    l.off_msh = rq_align256((uint64_t) M * K);
+    l.off_u = l.off_msh + rq_align256((uint64_t) M * (K / 64) * 4);
+    l.off_status = l.off_u + rq_align256((uint64_t) M * 4);
+    l.bytes = l.off_status + 256;
+    return l;
+}
+
+// Launchers (one per .cu file).  All enqueue on `stream` and return a cudaError_t.
+cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,
+                          float clip, int G, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,
+                          cudaStream_t stream);
+cudaError_t rq_launch_prepack(const rq_block * blocks, int64_t K, int64_t N, float * sw, uint8_t * w4, int8_t * w8,
+                              int8_t * wk, int wk_mode, cudaStream_t stream);
+cudaError_t rq_launch_scan_wk(const rq_block * blocks, int64_t n_blocks, int32_t * flag, cudaStream_t stream);
+cudaError_t rq_launch_gemv(const uint8_t * w4, const float * sw, const int8_t * wk, int64_t K, int64_t N,
+                           const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
+                           float * y, int64_t ldy, cudaStream_t stream);
+cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mode, int64_t K, int64_t N,
+                              const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
+                              float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
+// host-side: encodes the 2-D tensor map of a row-major int8 [rows][K] operand with a {128, box_rows} box, 128B swizzle
+int rq_encode_tmap_i8(void * tmap_out, const void * base, int64_t K, int64_t rows, int box_rows);

@@ -1,0 +1,72 @@
+// One-time re-layout of a W4A4 / W4A4H weight into what the contraction kernels stream.  The 144-byte blocks are only
+// read.  (The reference re-packs in place on first use: rq_repack_kernel / rq_colsum_kernel / rq_wk_kernel,
+// ggml/src/ggml-cuda/rq-w4a4.cu in patches/llama.cpp-ruquant.patch:1842-1880.)
+//
+//   sw  f32 [N]        the row unit s_w (block 0 of each row; every block of a row repeats it)
+//   w4  u32 [N][K/8]   decode stream: the 8 codes of a word re-ordered so that byte b holds code b in its low nibble
+//                      and code b+4 in its high nibble.  `w & 0xF0F0F0F0` is then the int8 vector 16*(c4..c7) and
+//                      `(w << 4) & 0xF0F0F0F0` the int8 vector 16*(c0..c3): two logic ops per 8 codes, no sign fix-up.
+//   w8  i8  [N][K]     tensor-core operand: 16*c when every multiplier is 1, else k*c (|k*c| <= 120)
+//   wk  i8  [N][K/64]  the multiplier of each run of 64 inputs (RQ_W_MULT_G, patch:40-43), only when some k != 1
+#include "rq_common.cuh"
+
+namespace {
+
+__global__ void rq_scan_wk_kernel(const rq_block * __restrict__ blocks, int64_t n_blocks, int32_t * flag) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_blocks) return;
+    const int32_t s = blocks[i].sum;
+    bool any = false;
+    for (int g = 0; g < 4; ++g) any |= rq_wmult(s, g) != 1;
+    if (any) atomicOr(flag, 1);
+}
+
+// a thread per (row, word of 8 codes)
+__global__ void rq_prepack_kernel(const rq_block * __restrict__ blocks, int64_t K, int64_t N, float * __restrict__ sw,
+                                  uint32_t * __restrict__ w4, int8_t * __restrict__ w8, int8_t * __restrict__ wk,
+                                  int wk_mode) {
+    const int64_t words = K / 8;
+    const int64_t idx = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= N * words) return;
+    const int64_t row = idx / words, w = idx - row * words;
+    const rq_block * b = blocks + row * (K / RQ_BLOCK_CODES) + w / 32;
+    const uint32_t src = b->qs[w % 32];
+    const int g64 = (int) ((w % 32) / 8);
+    const int k = rq_wmult(b->sum, g64);
+    if (w == 0) sw[row] = b->d;
+    if (wk != nullptr && (w % 8) == 0) wk[row * (K / 64) + w / 8] = (int8_t) k;
+    if (w4 != nullptr) {
+        uint32_t dst = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            dst |= ((src >> (4 * j)) & 0xFu) << (8 * j);
+            dst |= ((src >> (4 * (j + 4))) & 0xFu) << (8 * j + 4);
+        }
+        w4[row * words + w] = dst;
+    }
+    if (w8 != nullptr) {
+        const int mult = wk_mode ? k : RQ_W_SCALE;
+        uint32_t pk[2] = { 0u, 0u };
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = ((int) (((src >> (4 * j)) & 0xFu) << 28)) >> 28;
+            pk[j >> 2] |= (uint32_t) ((c * mult) & 0xFF) << (8 * (j & 3));
+        }
+        reinterpret_cast<uint2 *>(w8 + row * K)[w] = make_uint2(pk[0], pk[1]);
+    }
+}
+
+}  // namespace
+
+cudaError_t rq_launch_scan_wk(const rq_block * blocks, int64_t n_blocks, int32_t * flag, cudaStream_t stream) {
+    rq_scan_wk_kernel<<<(unsigned) ((n_blocks + 255) / 256), 256, 0, stream>>>(blocks, n_blocks, flag);
+    return cudaGetLastError();
+}
+
+cudaError_t rq_launch_prepack(const rq_block * blocks, int64_t K, int64_t N, float * sw, uint8_t * w4, int8_t * w8,
+                              int8_t * wk, int wk_mode, cudaStream_t stream) {
+    const int64_t n = N * (K / 8);
+    rq_prepack_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, stream>>>(blocks, K, N, sw, reinterpret_cast<uint32_t *>(w4),
+                                                                       w8, wk, wk_mode);
+    return cudaGetLastError();
+}

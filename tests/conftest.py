@@ -1,0 +1,26 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+@pytest.fixture(scope="session")
+def port():
+    import oracle
+    return oracle.Port()
+
+
+@pytest.fixture(scope="session")
+def ref():
+    import oracle
+    if not oracle.have_ref():
+        pytest.skip("oracle/_ref is not built (the reference tree is not present on this machine)")
+    return oracle.Ref()

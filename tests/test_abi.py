@@ -1,0 +1,66 @@
+"""CPU: the C-ABI library loads and exports every symbol include/rq_b200.h declares; host-only entry points behave."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "rq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(rq_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from ruquant_b200 import build
+    build.build()
+    import ruquant_b200
+    return ruquant_b200.lib()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), n
+    import ruquant_b200
+    assert sorted(ruquant_b200.EXPORTS) == [n for n in names if n in ruquant_b200.EXPORTS]
+    assert set(names) == set(ruquant_b200.EXPORTS)
+
+
+def test_supported_mirrors_reference_shape_rules(lib):
+    import ruquant_b200 as rq
+    assert rq.supported(44, 4096, 1024, 1)
+    assert rq.supported(45, 17408, 5120, 4096)
+    assert not rq.supported(45, 1792, 64, 1)          # no H_p x H_m factorisation
+    assert rq.supported(44, 1792, 64, 1)              # plain W4A4 does not rotate
+    assert not rq.supported(44, 4096 + 128, 64, 1)    # K not a multiple of 256
+    assert not rq.supported(44, 32768 + 256, 64, 1)   # K above the reference's 128 blocks
+    assert not rq.supported(43, 4096, 64, 1)
+    assert not rq.supported(44, 4096, 64, 1, ldx_bytes=4096 * 4 + 4)   # rows must stay 16-byte aligned
+    assert rq.supported(44, 4096, 136, 3)             # any N (the reference needs N % 32 == 0)
+
+
+def test_factor_and_sizes(lib):
+    import ruquant_b200 as rq
+    assert rq.hadamard_factor(5120) == (20, 256)
+    assert rq.hadamard_factor(17408) == (68, 256)
+    assert rq.hadamard_factor(1792) is None
+    K, N = 5120, 5120
+    assert lib.rq_w4a4_prepack_bytes(45, K, N, rq.PREPACK_DECODE) >= N * K // 2 + N * 4
+    assert lib.rq_w4a4_prepack_bytes(45, K, N, rq.PREPACK_ALL) >= N * K * 3 // 2
+    assert lib.rq_w4a4_prepack_bytes(45, K + 1, N, rq.PREPACK_ALL) == 0
+    assert rq.workspace_bytes(K, 64) >= 64 * K + 64 * (K // 64) * 4 + 64 * 4
+    assert lib.rq_status_string(-3).decode().startswith("W4A4H")
+
+
+def test_null_arguments_return_status_not_crash(lib):
+    # error behaviour: status codes where the reference aborts
+    assert lib.rq_w4a4_prepare(None, 44, 4096, 64, None, 0, 3, None, None) == -1
+    assert lib.rq_w4a4_mul_mat(None, 1, None, 0, 1, None, None, 1.0, 64, 0, None, 0, None) == -1
+    assert lib.rq_w4a4_quantize(None, 4096, 1, 4096, 0, 1.0, 64, None, 0, None) == -1
+    assert lib.rq_w4a4_rotate(None, 4096, 1, 4096, 4096, None, 4096, None) == -1
