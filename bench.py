@@ -1,0 +1,333 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4H MUL_MAT path:  python bench.py --gpus N --steps K --warmup W  [--impl reference]
+
+Workload (config.workload): the 64-layer 27B-shaped decoder linear stack in W4A4H -- per layer q 5120->6144,
+k 5120->1024, v 5120->1024, o 6144->5120, gate 5120->17408, up 5120->17408, down 17408->5120 -- run as M = 1 decode.
+A step is one pass over all 448 matmuls, every matmul on its own fp32 N(0,1) activation; weights are synthetic
+N(0, 0.02) rows rotated and quantized to W4A4H on the GPU (ruquant_b200.synth); 12.27 GB of weight blocks, so every
+step streams far more than the 126 MB L2.  `value` is algorithmic GB/s: sum over matmuls of
+N*(K/256)*144 + 4*M*K + 4*M*N bytes, divided by the step time, inputs resident in HBM.  `e2e` is the same pass
+through the C ABI with host buffers: pinned-host -> device copies of the step's activations and device -> host
+copies of its outputs inside the timed region.  `prefill` reports the M = 4096 gate/up-shaped GEMM
+(K=5120, N=17408) in TOPS, whole node (rotate + quantize + tcgen05 GEMM + fold + epilogue).
+
+With N GPUs the weight rows are sharded along N, the activation is replicated and each matmul's output is
+assembled with an NCCL all-gather (total work fixed: "strong" scaling).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYER = [("q", 5120, 6144), ("k", 5120, 1024), ("v", 5120, 1024), ("o", 6144, 5120), ("gate", 5120, 17408),
+         ("up", 5120, 17408), ("down", 17408, 5120)]
+PREFILL = ("gate_up", 5120, 17408, 4096)
+METRIC = "W4A4H decode GB/s @M=1 over the 64-layer 27B-shaped linear stack (prefill TOPS @M=4096 under 'prefill')"
+
+
+def algorithmic_bytes(K, N, M):
+    return N * (K // 256) * 144 + 4 * M * K + 4 * M * N
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm = sorted(float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------- reference arm
+
+def cpu_reference_layer(wb_host, x_host, threads):
+    """One decoder layer's seven matmuls at M = 1 on the host cores with the reference's own compiled code
+    (oracle/_ref) or, where that is absent, the oracle port.  Returns (seconds, kind)."""
+    import oracle
+    if oracle.have_ref():
+        impl, kind = oracle.Ref(), "reference"
+        run = lambda wb, K, x: impl.mul_mat(wb, 45, K, x, threads=threads)
+    else:
+        impl, kind = oracle.Port(), "port"
+        run = lambda wb, K, x: impl.mul_mat(wb, 45, K, x, threads=threads)
+    best = float("inf")
+    for _ in range(3):
+        t0 = time.perf_counter()
+        for (name, K, N), wb, x in zip(LAYER, wb_host, x_host):
+            run(wb, K, x)
+        best = min(best, time.perf_counter() - t0)
+    return best, kind
+
+
+def host_layer(seed=0):
+    """One layer of W4A4H weights quantized on the host by the oracle port (64 distinct rows per tensor, tiled, as
+    the reference's own bench does to bound generation time) and its activations."""
+    import numpy as np
+
+    import oracle
+    port = oracle.Port()
+    rng = np.random.default_rng(seed)
+    wbs, xs = [], []
+    for name, K, N in LAYER:
+        rows = port.quantize_weights(rng.normal(0, 0.02, (64, K)).astype(np.float32), 45)
+        wbs.append(np.tile(rows, (N // 64, 1)))
+        xs.append(rng.normal(0, 1, (1, K)).astype(np.float32))
+    return wbs, xs
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    wbs, xs = host_layer()
+    layer_bytes = sum(algorithmic_bytes(K, N, 1) for _, K, N in LAYER)
+    times = []
+    kind = None
+    for i in range(args.warmup + args.steps):
+        t, kind = cpu_reference_layer(wbs, xs, threads)
+        if i >= args.warmup:
+            times.append(t)
+    t = sum(times) / len(times)
+    gbs = layer_bytes / t / 1e9
+    sample = "1 of 64 layers per step (7 matmuls, M=1), best of 3 per step; GB/s is per-layer bytes / per-layer time"
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int4 x int4 -> int32, fp32 epilogue", "data": "synthetic",
+            "config": {"workload": "27B-shaped 64-layer W4A4H linear stack, M=1 decode (reference CPU path)", "layers_timed": 1},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------- our arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import ruquant_b200 as rq
+    from ruquant_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rq.lib()
+    hbm_peak, _, peak_kind = measured_peaks()
+    L = args.layers
+
+    # ---- the stack: rank r holds rows [r*N/g, (r+1)*N/g) of every tensor
+    mats = []          # (K, N_total, N_local, Weight, x_dev, y_local, y_full, workspace)
+    for layer in range(L):
+        for ti, (name, K, N) in enumerate(LAYER):
+            nl = N // world
+            blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=100000 * layer + 100 * ti + rank, device=dev)
+            w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_DECODE)
+            if layer > 0:
+                w.blocks = None      # the kernels read only the prepacked stream; layer 0's blocks feed the CPU baseline
+            del blocks
+            g = torch.Generator(device=dev)
+            g.manual_seed(7_000_000 + 10 * layer + ti)
+            x = torch.randn((1, K), generator=g, device=dev, dtype=torch.float32)
+            y_full = torch.empty((1, N), device=dev, dtype=torch.float32)
+            y_loc = y_full if world == 1 else torch.empty((1, nl), device=dev, dtype=torch.float32)
+            mats.append((K, N, nl, w, x, y_loc, y_full, rq.new_workspace(K, 1, dev)))
+    torch.cuda.synchronize()
+    total_bytes = sum(algorithmic_bytes(K, N, 1) for (K, N, *_r) in mats)
+    stream = torch.cuda.Stream(device=dev)
+
+    def enqueue_pass(quantize=True):
+        for K, N, nl, w, x, y_loc, y_full, ws in mats:
+            if quantize:
+                rq.mul_mat(w, x, out=y_loc, clip=1.0, act_group=64, workspace=ws, stream=stream)
+            else:
+                rq.mul_mat_quantized(w, 1, ws, out=y_loc, act_group=64, stream=stream)
+            if world > 1:
+                dist.all_gather_into_tensor(y_full.view(-1), y_loc.view(-1))
+
+    def capture(fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            fn()                      # warm: first-launch attribute set-up happens outside capture
+            stream.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+        return g
+
+    g_pass = capture(lambda: enqueue_pass(True))
+    g_gemv = capture(lambda: enqueue_pass(False)) if world == 1 else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_step = timed(g_pass.replay, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    value = total_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- dominant kernel alone: the 448 GEMV launches on already-quantized activations
+    roofline = None
+    if g_gemv is not None:
+        ms_gemv = timed(g_gemv.replay, args.steps, args.warmup)
+        achieved = total_bytes / (ms_gemv * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "rq_gemv_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": achieved / hbm_peak, "peak_kind": "of " + peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                    "avg_launch_us": ms_gemv * 1e3 / len(mats), "launches_per_step": len(mats),
+                    "algorithmic_bytes_per_launch": total_bytes / len(mats), "traffic": None}
+
+    # ---- end to end through the C ABI with host buffers
+    x_host = [torch.randn((1, K), dtype=torch.float32).pin_memory() for (K, *_r) in mats]
+    y_host = [torch.empty((1, N), dtype=torch.float32).pin_memory() for (_K, N, *_r) in mats]
+    h2d = sum(x.numel() * 4 for x in x_host)
+    d2h = sum(y.numel() * 4 for y in y_host)
+
+    def e2e_step():
+        for (K, N, nl, w, x, y_loc, y_full, ws), xh in zip(mats, x_host):
+            x.copy_(xh, non_blocking=True)
+        g_pass.replay()
+        for (K, N, nl, w, x, y_loc, y_full, ws), yh in zip(mats, y_host):
+            yh.copy_(y_full, non_blocking=True)
+
+    ms_e2e = timed(e2e_step, args.steps, args.warmup)
+    e2e = {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": ms_e2e}
+
+    # ---- prefill: M = 4096 gate/up-shaped GEMM, whole node and GEMM kernel alone
+    prefill = None
+    if not args.no_prefill:
+        _, K, N, M = PREFILL
+        nl = N // world
+        blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=424242 + rank, device=dev)
+        w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_PREFILL)
+        g = torch.Generator(device=dev)
+        g.manual_seed(99)
+        x = torch.randn((M, K), generator=g, device=dev, dtype=torch.float32)
+        y = torch.empty((M, nl), device=dev, dtype=torch.float32)
+        y_all = torch.empty((world, M, nl), device=dev, dtype=torch.float32) if world > 1 else None
+        ws = rq.new_workspace(K, M, dev)
+
+        def node():
+            rq.mul_mat(w, x, out=y, clip=1.0, act_group=64, workspace=ws, stream=stream)
+            if world > 1:
+                dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
+
+        def gemm_only():
+            rq.mul_mat_quantized(w, M, ws, out=y, act_group=64, stream=stream)
+
+        ms_node = timed(node, max(3, args.steps), 3)
+        ms_gemm = timed(gemm_only, max(3, args.steps), 3)
+        rq.device_status(ws, K, M)
+        ops = 2.0 * M * N * K
+        prefill = {"workload": "W4A4H K=5120 N=17408 M=4096", "tops_node": ops / (ms_node * 1e-3) / 1e12, "ms_node": ms_node,
+                   "tops_gemm_kernel": 2.0 * M * nl * K / (ms_gemm * 1e-3) / 1e12 * world, "ms_gemm_kernel": ms_gemm,
+                   "int8_dense_peak_nominal_tops": 4500.0 * world,
+                   "frac_of_nominal_int8_peak": ops / (ms_node * 1e-3) / 1e12 / (4500.0 * world)}
+
+    # ---- CPU baseline beside it (rank 0, one GPU): one layer on the host cores
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        wbs, xs = host_layer()
+        threads = os.cpu_count() or 1
+        t, kind = cpu_reference_layer(wbs, xs, threads)
+        layer_bytes = sum(algorithmic_bytes(K, N, 1) for _, K, N in LAYER)
+        cpu = {"value": layer_bytes / t / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+               "sample": "1 of 64 layers (7 matmuls, M=1), best of 3; per-layer bytes / per-layer time"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int4 x int4 -> int32, fp32 epilogue", "data": "synthetic",
+                "config": {"workload": "27B-shaped %d-layer W4A4H linear stack, M=1 decode, 7 matmuls per layer" % L,
+                           "weights_gb": sum(N * (K // 256) * 144 for (K, N, *_r) in mats) / 1e9,
+                           "l2": "inputs larger than L2 (weights streamed once per step)",
+                           "parallelism": "N-sharded x%d, NCCL all-gather per matmul" % world if world > 1 else "single GPU",
+                           "cuda_graph": True},
+                "frac_of_hbm_peak": value / (hbm_peak * world), "peak_kind": "of " + peak_kind,
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "prefill": prefill, "clocks": clocks,
+                "gpu_launches": 2 * len(mats) * args.steps}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

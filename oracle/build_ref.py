@@ -151,6 +151,7 @@ def main():
     cmd = ["gcc", "-O3", "-std=gnu11", "-fPIC", "-shared", "-fopenmp", "-fvisibility=default", "-o", so, src, "-lm"]
     print(" ".join(cmd))
     subprocess.check_call(cmd)
+    os.remove(src)   # keep only the library: the reference's lines do not stay on disk in this tree
     print("built", so)
     return 0
 

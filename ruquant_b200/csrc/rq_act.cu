@@ -229,13 +229,18 @@ __global__ void __launch_bounds__(ACT_THREADS) rq_act_kernel(const ActParams prm
 }
 
 template <int P>
+cudaError_t configure() {
+    return cudaFuncSetAttribute(rq_act_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, RQ_MAX_K * 4);
+}
+
+template <int P>
 cudaError_t launch(const ActParams & prm, int64_t M, size_t smem, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(rq_act_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, RQ_MAX_K * 4);
+        e = configure<P>();
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -244,6 +249,16 @@ cudaError_t launch(const ActParams & prm, int64_t M, size_t smem, cudaStream_t s
 }
 
 }  // namespace
+
+// opt every instantiation into the large dynamic shared memory carve-out (done by rq_w4a4_prepare, outside capture)
+cudaError_t rq_configure_act() {
+    cudaError_t e;
+    if ((e = configure<0>()) != cudaSuccess) return e;
+    if ((e = configure<1>()) != cudaSuccess) return e;
+    if ((e = configure<12>()) != cudaSuccess) return e;
+    if ((e = configure<20>()) != cudaSuccess) return e;
+    return configure<68>();
+}
 
 cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,
                           float clip, int G, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,

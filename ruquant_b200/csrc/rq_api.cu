@@ -122,6 +122,8 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_prepare(const void
 
     // block 0 of row 0 carries the tensor's switches (ggml_rq_tensor_clip / ggml_rq_tensor_rot, patch:2602-2610;
     // rq_info, patch:2027-2043): sum -> weight-group mode, pad[0] -> Hadamard length, pad[1] -> clip
+    RQ_CUDA(rq_configure_act());
+    RQ_CUDA(rq_configure_gemm_tc());
     rq_block hdr;
     uint8_t * pp = static_cast<uint8_t *>(prepack_dev);
     int32_t * flag_dev = reinterpret_cast<int32_t *>(pp + l.off_wk);   // scratch until the pack kernel overwrites it

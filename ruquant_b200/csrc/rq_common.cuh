@@ -60,5 +60,9 @@ cudaError_t rq_launch_gemv(const uint8_t * w4, const float * sw, const int8_t * 
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mode, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
+// per-device kernel attributes (large dynamic shared memory); called from rq_w4a4_prepare so that the first
+// launch inside a stream capture has nothing left to set up
+cudaError_t rq_configure_act();
+cudaError_t rq_configure_gemm_tc();
 // host-side: encodes the 2-D tensor map of a row-major int8 [rows][K] operand with a {128, box_rows} box, 128B swizzle
 int rq_encode_tmap_i8(void * tmap_out, const void * base, int64_t K, int64_t rows, int box_rows);

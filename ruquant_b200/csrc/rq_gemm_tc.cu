@@ -221,7 +221,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int buf = ag & 1;
             const int mm = WK ? (mnext >> RQ_MSH_SHIFT) : mnext;
             if (ag + 1 < n_ag) mnext = row_ok ? __ldg(mrow + ag + 1) : 0;
-            if (!mbar_wait(smem_u32(&sh.tmem_full[buf]), (ag >> 1) & 1, abort_flag)) { ok = false; break; }
+            // the loads below are warp-collective: leave the loop together or not at all
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_full[buf]), (ag >> 1) & 1, abort_flag))) { ok = false; break; }
             tc_fence_after();
             const uint32_t t0 = lane_base + (uint32_t) buf * BN;
 #pragma unroll
@@ -307,6 +308,12 @@ int rq_encode_tmap_i8(void * tmap_out, const void * base, int64_t K, int64_t row
     return 0;
 }
 
+cudaError_t rq_configure_gemm_tc() {
+    cudaError_t e = cudaFuncSetAttribute(rq_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(rq_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+}
+
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mode, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream) {
@@ -315,9 +322,7 @@ cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mod
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(rq_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(rq_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        e = rq_configure_gemm_tc();
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }

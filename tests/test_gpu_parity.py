@@ -1,0 +1,273 @@
+"""GPU: the CUDA path, called through the C ABI, against the oracle and the golden vectors -- bit for bit
+(tolerance 0, like the reference's own backend test: max_nmse_err() == 0.0 for W4A4 / W4A4H,
+tests/test-backend-ops.cpp hunk in patches/llama.cpp-ruquant.patch:2946-2948)."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from tests import inputs
+from tests.test_oracle_golden import CASE_CLIP, CASE_TYPES, ENV_SETTINGS, cases_of, load
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def rq():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import ruquant_b200
+    ruquant_b200.lib()       # raises if the extension is missing: there is no fallback to test
+    return ruquant_b200
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def gpu_mul_mat(rq, wb, type_, K, x, group=64, path=0, clip=None):
+    w = rq.Weight(dev(wb).view(-1), type_, K, N=wb.shape[0])
+    M = x.shape[0]
+    ws = rq.new_workspace(K, M)
+    y = rq.mul_mat(w, dev(x), act_group=group, path=path, clip=clip, workspace=ws)
+    torch.cuda.synchronize()
+    rq.device_status(ws, K, M)
+    return y.cpu().numpy()
+
+
+def assert_bits(got, want, what):
+    g, w = inputs.bits(got), inputs.bits(want) if want.dtype != np.uint32 else want
+    bad = np.argwhere(g != w)
+    assert bad.size == 0, "%s: %d of %d outputs differ, first at %s: got %r want %r" % (
+        what, len(bad), g.size, bad[0], got[tuple(bad[0])], w[tuple(bad[0])].view(np.float32))
+
+
+# ------------------------------------------------------------------------------------------- stages
+
+def test_rotation_matches_golden(rq):
+    g = load("default")
+    for n in (256, 1536, 5120, 6144, 11264, 17408):
+        got = rq.rotate(dev(g["rot%d_x" % n]), n).cpu().numpy()
+        assert_bits(got, g["rot%d_y" % n], "rotation n=%d" % n)
+
+
+def test_block_diagonal_rotation(rq, port):
+    # RQ_ROT_BLOCKS files: the Hadamard length is a divisor of K and each run of n_rot inputs rotates on its own
+    rng = np.random.default_rng(3)
+    for K, n_rot in [(5120, 2560), (6144, 1536), (4096, 1024), (17408, 4352)]:
+        x = rng.normal(0, 1, (3, K)).astype(np.float32)
+        assert_bits(rq.rotate(dev(x), n_rot).cpu().numpy(), port.rotate(x, n_rot), "K=%d n_rot=%d" % (K, n_rot))
+
+
+@pytest.mark.parametrize("group", [64, 128, 256])
+def test_activation_quantizer_fields(rq, port, group):
+    rng = np.random.default_rng(5)
+    for K, n_rot, clip in [(4096, 0, 1.0), (5120, 5120, 0.9), (6144, 6144, 1.0), (17408, 17408, 0.8), (256, 0, 0.7)]:
+        x = inputs.outlier_activations(5, K, 11)
+        x[1] = 0.0                      # an all-zero token: R == 0 -> 2
+        x[2, :K // 2] = 0.0             # groups with an empty range: m = 1
+        x[3] = np.abs(x[3])             # no negative values: z = 0
+        x[4] = rng.uniform(-1e-30, 1e-30, K).astype(np.float32)
+        ws, a8, msh, u = rq.quantize(dev(x), n_rot, clip, group)
+        torch.cuda.synchronize()
+        uo, mo, zo, qo = oracle.act_fields(port.quantize_act(x, clip, group, n_rot), group)
+        assert_bits(u.cpu().numpy(), uo, "unit")
+        assert (msh.cpu().numpy() == (mo << 21)).all(), "multipliers"
+        want = 8 * (qo - np.repeat(zo, group, axis=1))
+        assert (a8.cpu().numpy().astype(np.int32) == want).all(), "codes"
+
+
+# ------------------------------------------------------------------------------------------- golden MUL_MAT
+
+@pytest.mark.parametrize("path", [1, 2], ids=["gemv", "tcgen05"])
+@pytest.mark.parametrize("env", sorted(ENV_SETTINGS))
+def test_mul_mat_matches_golden(rq, env, path):
+    group = ENV_SETTINGS[env][0]
+    g, base = load(env), load("default")
+    for name in cases_of(g):
+        x, wb = base[name + "_x"], g[name + "_w"]
+        got = gpu_mul_mat(rq, wb, CASE_TYPES[name], x.shape[1], x, group=group, path=path)
+        assert_bits(got, g[name + "_y"], "%s/%s" % (env, name))
+
+
+# ------------------------------------------------------------------------------------------- the reference's own test shapes
+
+def ref_shape_list():
+    shapes = []
+    for n in (1, 3, 8, 17, 64, 200):
+        for k in (256, 512, 1536, 5120, 6144):
+            shapes.append((136, n, k))
+    shapes.append((5120, 32, 17408))
+    for n in (1, 2, 4, 5, 8, 16, 24, 32, 48, 64, 65, 130):
+        for k in (256, 6144):
+            shapes.append((256, n, k))
+    shapes += [(192, 8, 5120), (1024, 8, 5120), (5120, 8, 17408)]
+    return shapes
+
+
+@pytest.mark.parametrize("type_", [44, 45])
+def test_reference_backend_test_shapes(rq, port, type_):
+    # every (rows, tokens, K) of the reference's test list, with its adversarial initialiser, tolerance 0
+    for rows, tokens, K in ref_shape_list():
+        w = inputs.reference_test_weights(rows, K)
+        x = inputs.reference_test_activations(tokens, K, w, type_ == 44, 77)
+        wb = port.quantize_weights(w, type_)
+        want = port.mul_mat(wb, type_, K, x)
+        assert_bits(gpu_mul_mat(rq, wb, type_, K, x), want, "rows=%d tokens=%d K=%d" % (rows, tokens, K))
+
+
+# ------------------------------------------------------------------------------------------- configurations of the benchmark
+
+def test_config1_w4a4_decode(rq, port):
+    K, N = 4096, 1024
+    wb = oracle.set_clip(port.quantize_weights(inputs.normal_weights(N, K, 1000), 44), 1.0)
+    x = np.random.default_rng(1001).normal(0, 1, (1, K)).astype(np.float32)
+    assert_bits(gpu_mul_mat(rq, wb, 44, K, x), port.mul_mat(wb, 44, K, x), "config 1")
+
+
+@pytest.mark.parametrize("M", [1, 4, 16, 64])
+def test_config2_w4a4h_sweep(rq, port, M):
+    K = N = 5120
+    wb = oracle.set_clip(port.quantize_weights(inputs.normal_weights(N, K, 2000), 45), 0.9)
+    x = inputs.outlier_activations(M, K, 2001, 8, 40.0)
+    want = port.mul_mat(wb, 45, K, x)
+    assert_bits(gpu_mul_mat(rq, wb, 45, K, x), want, "config 2 M=%d auto" % M)
+    assert_bits(gpu_mul_mat(rq, wb, 45, K, x, path=1), want, "config 2 M=%d gemv" % M)
+    assert_bits(gpu_mul_mat(rq, wb, 45, K, x, path=2), want, "config 2 M=%d tcgen05" % M)
+
+
+def test_config3_prefill_full_size_sampled(rq, port):
+    # full K=5120 N=17408 M=4096 on the GPU; the oracle checks every output of a seeded sample of 192 tokens
+    K, N, M = 5120, 17408, 4096
+    wf = inputs.normal_weights(256, K, 3000)                 # 256 distinct rows, tiled
+    wb = np.tile(port.quantize_weights(wf, 45), (N // 256, 1))
+    x = inputs.student_t_activations(M, K, 3001, 16, 50.0)
+    got = gpu_mul_mat(rq, wb, 45, K, x)
+    pick = np.sort(np.random.default_rng(3002).choice(M, 192, replace=False))
+    assert_bits(got[pick], port.mul_mat(wb, 45, K, x[pick]), "config 3 sample")
+    # size-independent property: tiled weight rows give tiled outputs
+    assert (inputs.bits(got).reshape(M, N // 256, 256) == inputs.bits(got)[:, None, :256]).all()
+
+
+@pytest.mark.parametrize("M", [1, 2, 8, 32, 128, 512])
+def test_config4_down_projection(rq, port, M):
+    K, N = 17408, 5120
+    wf = inputs.normal_weights(512, K, 4000)
+    wb = np.tile(port.quantize_weights(wf, 45), (N // 512, 1))
+    v = wb.reshape(N, -1, 144)
+    clips = np.random.default_rng(4002).uniform(0.8, 1.0, N).astype(np.float32)
+    for r in range(N):    # per-row clips in the headers: only block 0 of row 0 counts (ggml_rq_tensor_clip)
+        v[r, :, 12:16] = np.frombuffer(clips[r].tobytes(), dtype=np.uint8)
+    x = inputs.spiky_activations(M, K, 4001)
+    want = port.mul_mat(wb, 45, K, x)
+    assert_bits(gpu_mul_mat(rq, wb, 45, K, x), want, "config 4 M=%d" % M)
+    if M == 8:
+        assert_bits(gpu_mul_mat(rq, wb, 45, K, x, clip=float(clips[0])), want, "explicit clip == row 0's clip")
+
+
+def test_config5_layer_shapes(rq, port):
+    # one decoder layer's seven projections, M = 1 and M = 80 (reduced N keeps the oracle quick; K is full size)
+    for name, K, N in [("q", 5120, 6144), ("k", 5120, 1024), ("v", 5120, 1024), ("o", 6144, 5120), ("gate", 5120, 17408),
+                       ("up", 5120, 17408), ("down", 17408, 5120)]:
+        wf = inputs.normal_weights(128, K, 5000 + N)
+        wb = np.tile(port.quantize_weights(wf, 45), (N // 128, 1))
+        for M in (1, 80):
+            x = np.random.default_rng(5001 + M).normal(0, 1, (M, K)).astype(np.float32)
+            assert_bits(gpu_mul_mat(rq, wb, 45, K, x), port.mul_mat(wb, 45, K, x), "%s M=%d" % (name, M))
+
+
+# ------------------------------------------------------------------------------------------- properties and edges
+
+def test_token_permutation_and_path_agreement(rq, port):
+    K, N, M = 6144, 768, 48
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 60), 45)
+    x = inputs.outlier_activations(M, K, 61)
+    perm = np.random.default_rng(62).permutation(M)
+    y = gpu_mul_mat(rq, wb, 45, K, x, path=2)
+    assert_bits(gpu_mul_mat(rq, wb, 45, K, x[perm], path=2), y[perm], "token permutation")
+    assert_bits(gpu_mul_mat(rq, wb, 45, K, x, path=1), y, "gemv == tcgen05")
+
+
+def test_row_sharding_is_exact(rq, port):
+    # weights sharded along N: each shard's output equals the matching columns of the unsharded result
+    K, N, M = 5120, 1024, 5
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 70), 45)
+    x = inputs.outlier_activations(M, K, 71)
+    full = gpu_mul_mat(rq, wb, 45, K, x)
+    for g in (2, 4, 8):
+        for r in range(g):
+            part = gpu_mul_mat(rq, wb[r * N // g:(r + 1) * N // g], 45, K, x)
+            assert_bits(part, full[:, r * N // g:(r + 1) * N // g], "shard %d/%d" % (r, g))
+
+
+def test_ragged_rows_strides_and_fused_weights(rq, port):
+    K, M = 1536, 7
+    x = inputs.outlier_activations(M, K, 81)
+    xs = torch.zeros((M, K + 64), dtype=torch.float32, device="cuda")
+    xs[:, :K] = dev(x)
+    weights, wants = [], []
+    for i, N in enumerate((8, 100, 260)):          # N not a multiple of the 256-row tile, nor of 4
+        wb = port.quantize_weights(inputs.normal_weights(N, K, 90 + i), 45)
+        weights.append(rq.Weight(dev(wb).view(-1), 45, K, N=N))
+        wants.append(port.mul_mat(wb, 45, K, x))
+    for path in (1, 2):
+        outs = [torch.full((M, w.N + 3), -7.0, dtype=torch.float32, device="cuda") for w in weights]
+        rq.mul_mat(weights, xs[:, :K], out=[o[:, :w.N] for o, w in zip(outs, weights)], path=path)
+        torch.cuda.synchronize()
+        for o, w, want in zip(outs, weights, wants):
+            assert_bits(o[:, :w.N].cpu().numpy(), want, "fused N=%d path=%d" % (w.N, path))
+            assert (o[:, w.N:] == -7.0).all(), "wrote past N"
+
+
+def test_cuda_graph_capture_and_replay(rq, port):
+    K, N, M = 5120, 512, 4
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 100), 45)
+    w = rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    x = torch.empty((M, K), dtype=torch.float32, device="cuda")
+    y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    ws = rq.new_workspace(K, M)
+    s = torch.cuda.Stream()
+    graphs = {}
+    for path in (1, 2):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
+                rq.mul_mat(w, x, out=y, workspace=ws, path=path, stream=s)
+        graphs[path] = g
+    for seed in (101, 102):
+        xh = inputs.outlier_activations(M, K, seed)
+        want = port.mul_mat(wb, 45, K, xh)
+        for path, g in graphs.items():
+            x.copy_(dev(xh))
+            y.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            assert_bits(y.cpu().numpy(), want, "graph replay path=%d" % path)
+
+
+def test_status_codes(rq, port):
+    K, N = 1792, 16          # 7 * 256: W4A4H cannot rotate this width
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 110), 44)
+    with pytest.raises(rq.RqError) as e:
+        rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    assert e.value.status == -3
+    w = rq.Weight(dev(wb).view(-1), 44, K, N=N)
+    x = torch.zeros((2, K), dtype=torch.float32, device="cuda")
+    with pytest.raises(rq.RqError) as e:
+        rq.mul_mat(w, x, act_group=32)
+    assert e.value.status == -4
+    with pytest.raises(rq.RqError) as e:
+        rq.mul_mat(w, x, clip=-1.0)
+    assert e.value.status == -9
+    with pytest.raises(rq.RqError) as e:
+        rq.mul_mat(w, x, workspace=torch.empty(256, dtype=torch.uint8, device="cuda"))
+    assert e.value.status == -5
+    g = load("wg64")
+    w64 = rq.Weight(dev(g["adv_w4a4_w"]).view(-1), 44, 512, N=40)
+    assert w64.desc.wg64 == 1 and w64.desc.wk_mode == 1
+    with pytest.raises(rq.RqError) as e:      # weight groups of 64 need activation groups of 64
+        rq.mul_mat(w64, torch.zeros((1, 512), dtype=torch.float32, device="cuda"), act_group=128)
+    assert e.value.status == -4
