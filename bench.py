@@ -313,6 +313,77 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_single(args):
+    """One shape, K,N,M[,type]: a CUDA graph of back-to-back matmuls over enough distinct weight copies to overflow
+    L2 (the method of the reference's own bench, rig/ggml_bench.cpp), whole node and contraction kernel alone."""
+    import torch
+
+    import ruquant_b200 as rq
+    from ruquant_b200 import synth
+
+    parts = [int(v) for v in args.single.split(",")]
+    K, N, M = parts[:3]
+    type_ = parts[3] if len(parts) > 3 else rq.TYPE_W4A4H
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    wbytes = N * (K // 256) * 144
+    copies = args.copies if args.copies > 0 else max(1, -(-(384 << 20) // wbytes)) if M <= 64 else 1
+    layouts = rq.PREPACK_ALL if args.path == 0 else (rq.PREPACK_DECODE if args.path == 1 else rq.PREPACK_PREFILL)
+    base = synth.random_weights(N, K, type_, seed=1, device=dev)
+    weights = []
+    for c in range(copies):
+        blocks = base if c == 0 else torch.roll(base, c, 0).contiguous()
+        w = rq.Weight(blocks.view(-1), type_, K, N=N, layouts=layouts)
+        w.blocks = None
+        weights.append(w)
+    del base
+    x = torch.randn((M, K), device=dev, dtype=torch.float32)
+    y = torch.empty((M, N), device=dev, dtype=torch.float32)
+    ws = rq.new_workspace(K, M, dev)
+    stream = torch.cuda.Stream(device=dev)
+    G = args.group
+
+    def node():
+        for w in weights:
+            rq.mul_mat(w, x, out=y, clip=1.0, act_group=G, path=args.path, workspace=ws, stream=stream)
+
+    def contraction():
+        for w in weights:
+            rq.mul_mat_quantized(w, M, ws, out=y, act_group=G, path=args.path, stream=stream)
+
+    def quant_only():
+        for w in weights:
+            rq.quantize(x, w.n_rot, 1.0, G, workspace=ws, stream=stream)
+
+    def timed(fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+            for _ in range(args.warmup):
+                g.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / args.steps / copies      # us per matmul
+
+    us_node, us_con, us_q = timed(node), timed(contraction), timed(quant_only)
+    rq.device_status(ws, K, M)
+    hbm_peak, _, kind = measured_peaks()
+    ab, ops = algorithmic_bytes(K, N, M), 2.0 * M * N * K
+    print(json.dumps({"single": {"K": K, "N": N, "M": M, "type": type_, "group": G, "path": args.path, "copies": copies},
+                      "us_node": us_node, "us_contraction": us_con, "us_rotate_quantize": us_q,
+                      "GBps_node": ab / us_node / 1e3, "GBps_contraction": ab / us_con / 1e3,
+                      "frac_hbm_node": ab / us_node / 1e3 / hbm_peak, "frac_hbm_contraction": ab / us_con / 1e3 / hbm_peak,
+                      "TOPS_node": ops / us_node / 1e6, "TOPS_contraction": ops / us_con / 1e6, "peak_kind": "of " + kind}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -322,8 +393,14 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--single", default="", help="K,N,M[,type]: time one shape instead of the stack")
+    ap.add_argument("--copies", type=int, default=0)
+    ap.add_argument("--group", type=int, default=64)
+    ap.add_argument("--path", type=int, default=0)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.single:
+        run_single(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
