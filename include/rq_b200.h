@@ -140,6 +140,15 @@ int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off
  * up on a bounded wait.  Not capture-safe. */
 int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream);
 
+/* No counterpart in the reference.  The MUL_MAT node for callers that may not allocate device memory (a backend
+ * whose buffers are planned ahead of time, a plug-in inside another runtime's stream): the scratch that
+ * rq_w4a4_mul_mat takes from the caller lives in a fixed array inside the library instead.  One weight, M <= 16
+ * tokens, K <= 32768, else RQ_ERR_LIMIT.  Calls no cudaMalloc / cudaFree.  All calls on a device share the array:
+ * calls that can overlap on the GPU race.  The first call on a device resolves the array's device address and
+ * should be made outside stream capture. */
+int rq_w4a4_mul_mat_static(const rq_weight_desc * w, const float * x_dev, int64_t ldx, int64_t M, float * y_dev, int64_t ldy,
+                           float clip, int act_group, int path, void * stream);
+
 const char * rq_status_string(int status);
 int rq_last_cuda_error(void);   /* cudaError_t of the last failed runtime call on this thread */
 

@@ -20,6 +20,7 @@ EXPORTS = [
     "rq_w4a4_supported", "rq_hadamard_factor", "rq_w4a4_resolve_clip", "rq_w4a4_act_group", "rq_w4a4_prepack_bytes",
     "rq_w4a4_prepare", "rq_w4a4_workspace_bytes", "rq_w4a4_mul_mat", "rq_w4a4_mul_mat_quantized", "rq_w4a4_rotate",
     "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
+    "rq_w4a4_mul_mat_static",
 ]
 
 
@@ -65,6 +66,7 @@ def lib():
         L.rq_w4a4_workspace_bytes.restype = sz
         L.rq_w4a4_mul_mat.argtypes = [ctypes.POINTER(pd), i32, vp, i64, i64, ctypes.POINTER(vp), ctypes.POINTER(i64), f32, i32,
                                       i32, vp, sz, vp]
+        L.rq_w4a4_mul_mat_static.argtypes = [pd, vp, i64, i64, vp, i64, f32, i32, i32, vp]
         L.rq_w4a4_mul_mat_quantized.argtypes = [pd, i64, vp, i64, i32, i32, vp, sz, vp]
         L.rq_w4a4_rotate.argtypes = [vp, i64, i64, i64, i64, vp, i64, vp]
         L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, vp, sz, vp]
@@ -181,6 +183,24 @@ def mul_mat(weights, x, out=None, clip=None, act_group=None, path=PATH_AUTO, wor
         _check(lib().rq_w4a4_mul_mat(descs, n_w, x.data_ptr(), x.stride(0), M, ys, ldy, clip, act_group, path,
                                      workspace.data_ptr(), workspace.numel(), _stream_ptr(stream)), "rq_w4a4_mul_mat")
     return outs[0] if single else outs
+
+
+def mul_mat_static(weight, x, out=None, clip=None, act_group=None, path=PATH_AUTO, stream=None):
+    """MUL_MAT without a caller workspace and without any allocation by the library: the scratch is a fixed array
+    inside librq_b200.so (one weight, at most 16 tokens).  For hosts that cannot allocate device memory; calls on one
+    device share the array, so do not let two of them overlap on the GPU."""
+    import torch
+    M, K = x.shape
+    if out is None:
+        out = torch.empty((M, weight.N), dtype=torch.float32, device=x.device)
+    if clip is None:
+        clip = weight.clip()
+    if act_group is None:
+        act_group = lib().rq_w4a4_act_group()
+    with torch.cuda.device(x.device):
+        _check(lib().rq_w4a4_mul_mat_static(ctypes.byref(weight.desc), x.data_ptr(), x.stride(0), M, out.data_ptr(),
+                                            out.stride(0), clip, act_group, path, _stream_ptr(stream)), "rq_w4a4_mul_mat_static")
+    return out
 
 
 def rotate(x, n_rot, stream=None):
