@@ -131,8 +131,9 @@ int rq_w4a4_rotate(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64
 int rq_w4a4_quantize(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float clip, int act_group,
                      void * workspace_dev, size_t workspace_bytes, void * stream);
 
-/* Where the quantized activation sits in the workspace: a8 = int8 [M][K] holding 8*(q - z_g); msh = int32
- * [M][K/act_group] holding m_g << 21; u = f32 [M] token units. */
+/* Where the quantized activation sits in the workspace: a8 = int8 [M][K] holding 8*(q - z_g),
+ * permuted inside each run of 64 inputs (piece 16*i + 4*t .. +3 at byte 16*t + 4*i); msh = int32
+ * [M][K/act_group] holding m_g; u = f32 [M] token units. */
 int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off_a8, uint64_t * off_msh, uint64_t * off_u,
                              uint64_t * off_status);
 

@@ -1,102 +1,78 @@
-// Activation side of the W4A4 / W4A4H MUL_MAT node: online Hadamard rotation + per-token grouped int4 quantizer,
-// one kernel, one CTA per token, the token's row resident in shared memory from load to store.
+// Activation side of the W4A4 / W4A4H MUL_MAT node: online Hadamard rotation + per-token grouped int4 quantizer.
 //
 // Bit-parity contract (reference: patches/llama.cpp-ruquant.patch, "patch" below):
 //   rotation   ggml_rq_hadamard, patch:2450-2485 -- Sylvester butterflies in increasing stride over each chunk of m,
 //              then every Paley output summed from 0.0f over ascending i with one add or subtract per term, then one
-//              multiply by 1/sqrtf(n).  Every fp32 operation here is an explicit round-to-nearest intrinsic so that
-//              nothing is contracted or reassociated.
+//              multiply by 1/sqrtf(n).  Every fp32 operation here is an explicit round-to-nearest intrinsic.  A term
+//              is applied as fma(x, +-1.0f, acc): the product is exact, so the result is the same single rounding as
+//              acc + x / acc - x, and the sign becomes data (a table in shared memory) instead of code.
 //   quantizer  rq_quantize_row_a, patch:2639-2679.
-// The kernel writes the activation in the layout the contraction kernels consume: int8 8*(q - z_g) [M][K],
-// int32 m_g << 21 [M][K/G], f32 u [M].
-#include <utility>
+// Output layout (what the contraction kernels consume): int8 8*(q - z_g) [M][K] (permuted inside each run of 64
+// inputs, see rq_perm64), int32 m_g [M][K/G], f32 u [M].
+//
+// Two kernels:
+//   rq_act_kernel<P>          one CTA per token, the token's row resident in shared memory (prefill widths, any G).
+//   rq_act_cluster_kernel<P>  a thread-block cluster per token for decode widths: the CTAs transform disjoint chunks,
+//                             exchange columns through distributed shared memory, split the Paley outputs between
+//                             them and agree on the token's range with one more cluster barrier.
+// Both start their successor early (programmatic dependent launch) and build the sign table before they wait for
+// the kernel that produced x.
+#include <cooperative_groups.h>
+
+#include <stdlib.h>
 
 #include "rq_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
 constexpr int ACT_THREADS = 256;
 
-// bit r of (LO, HI) is set when r is a non-zero square mod q: the Legendre symbol chi(r) = +1
-constexpr unsigned long long qr_bits(int q, int half) {
-    unsigned long long b = 0;
-    for (int i = 1; i < q; ++i) {
-        const int r = (i * i) % q;
-        if (r / 64 == half) b |= 1ull << (r % 64);
+// ---- Paley-I signs: A = I + S, S[0][a>0] = +1, S[i>0][0] = -1, S[i][a] = chi((a - i) mod q)   (rq_paley, patch:2432-2448)
+// table[i * p + a] = +1.0f / -1.0f for "add" / "subtract" of input chunk i into output chunk a
+__device__ void build_sign_table(float * table, signed char * chi, int p, int tid, int nt) {
+    const int q = p - 1;
+    for (int r = tid; r < q; r += nt) chi[r] = r == 0 ? 0 : -1;
+    __syncthreads();
+    for (int r = tid + 1; r < q; r += nt) chi[(r * r) % q] = 1;
+    __syncthreads();
+    for (int e = tid; e < p * p; e += nt) {
+        const int i = e / p, a = e - i * p;
+        bool plus;
+        if (i == a || i == 0) plus = true;
+        else if (a == 0) plus = false;
+        else plus = chi[(((a - i) % q) + q) % q] > 0;
+        table[e] = plus ? 1.0f : -1.0f;
     }
-    return b;
 }
 
-// Sign of entry (i, a) of the Paley-I matrix A = I + S of order P (rq_paley, patch:2432-2448):
-// S[0][a>0] = +1, S[i>0][0] = -1, S[i][a] = chi((a - i) mod q), and the diagonal of A is +1.
-template <int P, int I, int A>
-struct PaleySign {
-    static constexpr int Q = P - 1;
-    static constexpr int R = ((A - I) % Q + Q) % Q;
-    static constexpr bool plus = (I == A) ? true : (I == 0) ? true : (A == 0) ? false
-                                 : ((R < 64 ? (qr_bits(Q, 0) >> (R % 64)) : (qr_bits(Q, 1) >> (R % 64))) & 1ull) != 0;
-};
-
-template <int P, int A, int... I>
-__device__ __forceinline__ float paley_output(const float (&col)[P], std::integer_sequence<int, I...>) {
-    float acc = 0.0f;
-    ((acc = PaleySign<P, I, A>::plus ? __fadd_rn(acc, col[I]) : __fsub_rn(acc, col[I])), ...);
-    return acc;
-}
-
-template <int P, int... A>
-__device__ __forceinline__ void paley_column(const float (&col)[P], float * b, int m, float scale,
-                                             std::integer_sequence<int, A...>) {
-    ((b[A * m] = __fmul_rn(paley_output<P, A>(col, std::make_integer_sequence<int, P>{}), scale)), ...);
-}
-
-// Paley stage for a compile-time order: a thread owns column j of one rotation block, holds its P inputs in
-// registers and emits the P outputs with every sign folded at compile time (one FADD per term).
+// outputs a0 .. a0+3 of one column held in registers: four independent chains, terms in ascending i
 template <int P>
-__device__ __forceinline__ void paley_fixed(float * buf, int K, int n, int m, float scale, int tid, int nt) {
-    const int ncol = K / P;
-    for (int c = tid; c < ncol; c += nt) {
-        const int blk = c / m, j = c - blk * m;
-        float * b = buf + (size_t) blk * n + j;
-        float col[P];
+__device__ __forceinline__ void paley_block4(const float (&col)[P], const float * __restrict__ table, int a0, float scale,
+                                             float (&out)[4]) {
+    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
 #pragma unroll
-        for (int i = 0; i < P; ++i) col[i] = b[i * m];
-        paley_column<P>(col, b, m, scale, std::make_integer_sequence<int, P>{});
+    for (int i = 0; i < P; ++i) {
+        const float4 s = *reinterpret_cast<const float4 *>(table + i * P + a0);
+        acc0 = __fmaf_rn(col[i], s.x, acc0);
+        acc1 = __fmaf_rn(col[i], s.y, acc1);
+        acc2 = __fmaf_rn(col[i], s.z, acc2);
+        acc3 = __fmaf_rn(col[i], s.w, acc3);
     }
+    out[0] = __fmul_rn(acc0, scale);
+    out[1] = __fmul_rn(acc1, scale);
+    out[2] = __fmul_rn(acc2, scale);
+    out[3] = __fmul_rn(acc3, scale);
 }
 
-// Any order up to 128 (the factorisation admits 12, 20, 44, 60, 68, 72, 84, 104, 108): signs from a Legendre table
-// in shared memory, outputs parked in local memory until the column has been read for the last time.
-__device__ void paley_generic(float * buf, int K, int n, int p, int m, float scale, const signed char * chi, int tid,
-                              int nt) {
-    const int ncol = K / p, q = p - 1;
-    float out[128];
-    for (int c = tid; c < ncol; c += nt) {
-        const int blk = c / m, j = c - blk * m;
-        float * b = buf + (size_t) blk * n + j;
-        for (int a = 0; a < p; ++a) {
-            float acc = 0.0f;
-            for (int i = 0; i < p; ++i) {
-                bool plus;
-                if (i == a || i == 0) plus = true;
-                else if (a == 0) plus = false;
-                else plus = chi[(((a - i) % q) + q) % q] > 0;
-                const float v = b[i * m];
-                acc = plus ? __fadd_rn(acc, v) : __fsub_rn(acc, v);
-            }
-            out[a] = acc;
-        }
-        for (int a = 0; a < p; ++a) b[a * m] = __fmul_rn(out[a], scale);
-    }
-}
-
-// One radix-R pass of the Sylvester transform over every chunk: elements base + j*s, j < R, go through log2(R)
-// butterfly stages of strides s, 2s, 4s (the reference's order, h ascending; each stage is c[k] = a + b,
+// One radix-R pass of the Sylvester transform over a buffer of whole chunks: elements base + j*s, j < R, go through
+// log2(R) butterfly stages of strides s, 2s, 4s (the reference's order, h ascending; each stage is c[k] = a + b,
 // c[k+h] = a - b with k the lower index, patch:2456-2463).
 template <int R>
-__device__ __forceinline__ void fwht_pass(float * buf, int K, int ls, int tid, int nt) {
+__device__ __forceinline__ void fwht_pass(float * buf, int len, int ls, int tid, int nt) {
     const int s = 1 << ls;
-    for (int q = tid; q < K / R; q += nt) {
+    for (int q = tid; q < len / R; q += nt) {
         const int hi = q >> ls, lo = q & (s - 1);
         float * b = buf + (size_t) hi * s * R + lo;
         float v[R];
@@ -118,6 +94,149 @@ __device__ __forceinline__ void fwht_pass(float * buf, int K, int ls, int tid, i
     }
 }
 
+__device__ __forceinline__ void fwht_chunks(float * buf, int len, int m, int tid, int nt) {
+    for (int ls = 0; (1 << ls) < m; ls += 3) {
+        const int rem = m >> ls;
+        if (rem >= 8) fwht_pass<8>(buf, len, ls, tid, nt);
+        else if (rem == 4) fwht_pass<4>(buf, len, ls, tid, nt);
+        else fwht_pass<2>(buf, len, ls, tid, nt);
+        __syncthreads();
+    }
+}
+
+// Sylvester transform of 32*EPT consecutive values held by one warp, lane l owning values [l*EPT, (l+1)*EPT): the
+// strides below EPT are butterflies between a lane's own registers, the strides EPT .. 16*EPT are exchanges with lane
+// l ^ d (the lower lane forms a + b, the upper lane a - b with a the lower lane's value) -- the same operations in the
+// same order as the reference's loop, without touching shared memory.
+template <int EPT>
+__device__ __forceinline__ void fwht_warp(float (&v)[EPT], int lane) {
+#pragma unroll
+    for (int d = 1; d < EPT; d <<= 1) {
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            if ((j & d) == 0) {
+                const float a = v[j], c = v[j + d];
+                v[j] = __fadd_rn(a, c);
+                v[j + d] = __fsub_rn(a, c);
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const bool upper = (lane & d) != 0;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], d);
+            v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+        }
+    }
+}
+
+// global -> (transform) -> shared for `count` runs of 32*EPT floats, one warp per run
+template <int EPT>
+__device__ __forceinline__ void load_transform_runs(const float * __restrict__ src, float * dst, int count, bool transform,
+                                                    int warp, int nwarps, int lane) {
+    for (int r = warp; r < count; r += nwarps) {
+        const float * s = src + (size_t) r * 32 * EPT + lane * EPT;
+        float * d = dst + (size_t) r * 32 * EPT + lane * EPT;
+        float v[EPT];
+        if constexpr (EPT >= 4) {
+#pragma unroll
+            for (int j = 0; j < EPT; j += 4) {
+                const float4 q = __ldg(reinterpret_cast<const float4 *>(s + j));
+                v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) v[j] = __ldg(s + j);
+        }
+        if (transform) fwht_warp<EPT>(v, lane);
+        if constexpr (EPT >= 4) {
+#pragma unroll
+            for (int j = 0; j < EPT; j += 4) *reinterpret_cast<float4 *>(d + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) d[j] = v[j];
+        }
+    }
+}
+
+// A buffer of `len` floats made of whole chunks of m: loaded from global memory and Sylvester-transformed chunk by
+// chunk.  Chunks up to 1024 wide are done entirely in registers and shuffles; wider chunks finish their upper
+// strides (1024 and above, conflict-free) in shared memory.  Ends with a CTA barrier.
+__device__ __forceinline__ void load_fwht(const float * __restrict__ src, float * dst, int len, int m, int tid, int nt) {
+    const int warp = tid >> 5, nwarps = nt >> 5, lane = tid & 31;
+    const int run = m < 1024 ? m : 1024;
+    switch (run) {
+        case 32:   load_transform_runs<1>(src, dst, len / 32, m > 1, warp, nwarps, lane); break;
+        case 64:   load_transform_runs<2>(src, dst, len / 64, true, warp, nwarps, lane); break;
+        case 128:  load_transform_runs<4>(src, dst, len / 128, true, warp, nwarps, lane); break;
+        case 256:  load_transform_runs<8>(src, dst, len / 256, true, warp, nwarps, lane); break;
+        case 512:  load_transform_runs<16>(src, dst, len / 512, true, warp, nwarps, lane); break;
+        case 1024: load_transform_runs<32>(src, dst, len / 1024, true, warp, nwarps, lane); break;
+        default: {   // m < 32 (1 .. 16): plain copy, then the generic passes
+            for (int i = tid; i < len; i += nt) dst[i] = __ldg(src + i);
+            __syncthreads();
+            fwht_chunks(dst, len, m, tid, nt);
+            return;
+        }
+    }
+    __syncthreads();
+    for (int ls = 10; (1 << ls) < m; ls += 3) {
+        const int rem = m >> ls;
+        if (rem >= 8) fwht_pass<8>(dst, len, ls, tid, nt);
+        else if (rem == 4) fwht_pass<4>(dst, len, ls, tid, nt);
+        else fwht_pass<2>(dst, len, ls, tid, nt);
+        __syncthreads();
+    }
+}
+
+// the chunks a cluster CTA owns (global chunk rank + s*C -> local slot s), one warp per run of 32*EPT values
+template <int EPT>
+__device__ __forceinline__ void cluster_chunks(const float * __restrict__ xrow, float * chunks, int rank, int C, int nloc, int m,
+                                               int tid, int nt) {
+    const int warp = tid >> 5, nwarps = nt >> 5, lane = tid & 31;
+    const int rpc = m / (32 * EPT);                          // runs per chunk (1 up to m = 1024)
+    for (int r = warp; r < nloc * rpc; r += nwarps) {
+        const int s = r / rpc, sr = r - s * rpc;
+        load_transform_runs<EPT>(xrow + (size_t) (rank + s * C) * m + (size_t) sr * 32 * EPT,
+                                 chunks + (size_t) s * m + (size_t) sr * 32 * EPT, 1, true, 0, 1, lane);
+    }
+}
+
+// ---- quantizer pieces shared by both kernels
+
+// range of a word of 8 values reduced over the lpg lanes that share its group
+__device__ __forceinline__ void group_range(const float4 a, const float4 b, int lpg, float clip, float & lo, float & hi) {
+    float mn = fminf(fminf(fminf(a.x, a.y), fminf(a.z, a.w)), fminf(fminf(b.x, b.y), fminf(b.z, b.w)));
+    float mx = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+    mn = fminf(mn, 0.0f);
+    mx = fmaxf(mx, 0.0f);
+    for (int o = 1; o < lpg; o <<= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    lo = __fmul_rn(mn, clip);
+    hi = __fmul_rn(mx, clip);
+}
+
+// the 8 codes of a word as int8 8*(q - z) and the group's multiplier
+__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, int & mi) {
+    const float mf = fminf(fmaxf(ceilf(__fdiv_rn(__fmul_rn(__fsub_rn(hi, lo), 255.0f), R)), 1.0f), 255.0f);
+    mi = (int) mf;
+    const float inv = __fdiv_rn(1.0f, __fmul_rn((float) mi, unit));
+    const float zf = fminf(fmaxf(rintf(__fmul_rn(-lo, inv)), 0.0f), 15.0f);
+    const float v[8] = { a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w };
+    uint32_t pk[2] = { 0u, 0u };
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float qf = fminf(fmaxf(__fadd_rn(rintf(__fmul_rn(v[j], inv)), zf), 0.0f), 15.0f);
+        const int d = RQ_ACT_SCALE * ((int) qf - (int) zf);   // 8*(q - z) in [-120, 120]
+        pk[j >> 2] |= (uint32_t) (d & 0xFF) << (8 * (j & 3));
+    }
+    return make_uint2(pk[0], pk[1]);
+}
+
 struct ActParams {
     const float * x;
     int64_t ldx;
@@ -128,10 +247,12 @@ struct ActParams {
     float * u;
     float * rot_out;
     int64_t ldo;
+    int32_t * status;
 };
 
-// P > 1: compile-time Paley order; P == 1: no Paley stage (plain W4A4, or a power-of-two rotation);
-// P == 0: run-time order prm.p.
+// =====================================================================================  one CTA per token
+// P > 1: Paley order (compile time); P == 1: no Paley stage (plain W4A4, or a power-of-two rotation).
+// shared memory: [K floats row][P*P floats sign table]
 template <int P>
 __global__ void __launch_bounds__(ACT_THREADS) rq_act_kernel(const ActParams prm) {
     extern __shared__ __align__(16) float buf[];
@@ -140,30 +261,38 @@ __global__ void __launch_bounds__(ACT_THREADS) rq_act_kernel(const ActParams prm
     __shared__ signed char chi[128];
     const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int K = prm.K;
+    float * table = buf + K;
 
-    const float4 * xr = reinterpret_cast<const float4 *>(prm.x + (int64_t) t * prm.ldx);
-    for (int i = tid; i < K / 4; i += nt) reinterpret_cast<float4 *>(buf)[i] = __ldg(xr + i);
-    if (P == 0) {
-        const int q = prm.p - 1;
-        if (tid < 128) chi[tid] = tid == 0 ? 0 : -1;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if constexpr (P > 1) build_sign_table(table, chi, P, tid, nt);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (t == 0 && tid == 0 && prm.status != nullptr) *prm.status = 0;
+
+    const float * xrow = prm.x + (int64_t) t * prm.ldx;
+    if (prm.n_rot > 0) {
+        load_fwht(xrow, buf, K, prm.m, tid, nt);
+    } else {
+        for (int i = tid; i < K / 4; i += nt) reinterpret_cast<float4 *>(buf)[i] = __ldg(reinterpret_cast<const float4 *>(xrow) + i);
         __syncthreads();
-        if (tid >= 1 && tid < q) chi[(tid * tid) % q] = 1;
     }
-    __syncthreads();
 
     if (prm.n_rot > 0) {
         const int m = prm.m;
-        for (int ls = 0; (1 << ls) < m; ls += 3) {
-            const int rem = m >> ls;
-            if (rem >= 8) fwht_pass<8>(buf, K, ls, tid, nt);
-            else if (rem == 4) fwht_pass<4>(buf, K, ls, tid, nt);
-            else fwht_pass<2>(buf, K, ls, tid, nt);
-            __syncthreads();
-        }
-        if (P > 1) {
-            paley_fixed<(P > 1 ? P : 12)>(buf, K, prm.n_rot, m, prm.rot_scale, tid, nt);
-        } else if (P == 0) {
-            paley_generic(buf, K, prm.n_rot, prm.p, m, prm.rot_scale, chi, tid, nt);
+        if constexpr (P > 1) {
+            const int ncol = K / P, n = prm.n_rot;
+            for (int c = tid; c < ncol; c += nt) {
+                const int blk = c / m, j = c - blk * m;
+                float * b = buf + (size_t) blk * n + j;
+                float col[P];
+#pragma unroll
+                for (int i = 0; i < P; ++i) col[i] = b[i * m];
+                for (int a0 = 0; a0 < P; a0 += 4) {
+                    float out[4];
+                    paley_block4<P>(col, table, a0, prm.rot_scale, out);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) b[(a0 + k) * m] = out[k];
+                }
+            }
         } else {
             for (int i = tid; i < K; i += nt) buf[i] = __fmul_rn(buf[i], prm.rot_scale);
         }
@@ -177,19 +306,10 @@ __global__ void __launch_bounds__(ACT_THREADS) rq_act_kernel(const ActParams prm
 
     // ---- quantizer: a thread owns a word of 8 values, G/8 neighbouring lanes own a group
     const int lpg = prm.G >> 3, nwords = K >> 3;
-    const float clip = prm.clip;
     float tmax = 0.0f;
     for (int w = tid; w < nwords; w += nt) {
-        const float4 a = reinterpret_cast<float4 *>(buf)[2 * w], b = reinterpret_cast<float4 *>(buf)[2 * w + 1];
-        float mn = fminf(fminf(fminf(a.x, a.y), fminf(a.z, a.w)), fminf(fminf(b.x, b.y), fminf(b.z, b.w)));
-        float mx = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
-        mn = fminf(mn, 0.0f);
-        mx = fmaxf(mx, 0.0f);
-        for (int o = 1; o < lpg; o <<= 1) {
-            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        }
-        const float lo = __fmul_rn(mn, clip), hi = __fmul_rn(mx, clip);
+        float lo, hi;
+        group_range(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1], lpg, prm.clip, lo, hi);
         if ((w & (lpg - 1)) == 0) {
             g_lo[w / lpg] = lo;
             g_hi[w / lpg] = hi;
@@ -209,32 +329,182 @@ __global__ void __launch_bounds__(ACT_THREADS) rq_act_kernel(const ActParams prm
     int32_t * mrow = prm.msh + (int64_t) t * (K / prm.G);
     for (int w = tid; w < nwords; w += nt) {
         const int g = w / lpg;
-        const float lo = g_lo[g], hi = g_hi[g];
-        const float mf = fminf(fmaxf(ceilf(__fdiv_rn(__fmul_rn(__fsub_rn(hi, lo), 255.0f), R)), 1.0f), 255.0f);
-        const int mi = (int) mf;
-        const float inv = __fdiv_rn(1.0f, __fmul_rn((float) mi, unit));
-        const float zf = fminf(fmaxf(rintf(__fmul_rn(-lo, inv)), 0.0f), 15.0f);
-        const float4 a = reinterpret_cast<float4 *>(buf)[2 * w], b = reinterpret_cast<float4 *>(buf)[2 * w + 1];
-        const float v[8] = { a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w };
-        uint32_t pk[2] = { 0u, 0u };
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float qf = fminf(fmaxf(__fadd_rn(rintf(__fmul_rn(v[j], inv)), zf), 0.0f), 15.0f);
-            const int d = RQ_ACT_SCALE * ((int) qf - (int) zf);   // 8*(q - z) in [-120, 120]
-            pk[j >> 2] |= (uint32_t) (d & 0xFF) << (8 * (j & 3));
-        }
-        reinterpret_cast<uint2 *>(arow)[w] = make_uint2(pk[0], pk[1]);
-        if ((w & (lpg - 1)) == 0) mrow[g] = mi << RQ_MSH_SHIFT;
+        int mi;
+        const uint2 pk = encode_word(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1],
+                                     g_lo[g], g_hi[g], R, unit, mi);
+        const int kw = w * 8, run = kw & ~63, off = kw & 63;   // two 4-input pieces, permuted inside their run of 64
+        *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off)) = pk.x;
+        *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off + 4)) = pk.y;
+        if ((w & (lpg - 1)) == 0) mrow[g] = mi;
     }
 }
 
+// =====================================================================================  a cluster per token
+// For G = 64, m a multiple of 64 and P > 1.  C = gridDim.x CTAs per token (8 or a smaller power of two).
+//   chunk ch = blk * P + i (m floats) is loaded and transformed by CTA ch % C into its slot ch / C;
+//   slice sl = blk * (m/64) + js owns columns [64 js, 64 js + 64) of block blk; T = K / (64 P) slices.
+//   With C >= T, cps = C / T CTAs share a slice and deal its NB = P / 4 blocks of 4 outputs round-robin; with C < T a
+//   CTA walks nsl = T / C slices and forms all their outputs.  Per slice the CTA first copies the slice's P x 64
+//   inputs out of the owners' shared memory (distributed shared memory, 256-byte rows), then a thread = (column,
+//   block slot) forms 4 outputs from registers; a row of 64 outputs is one activation group.
+// shared memory: [slots * m chunks][P*P sign table][P * 64 slice][nsl * nb_max * 4 * 64 outputs]
+template <int P>
+__global__ void __launch_bounds__(ACT_THREADS) rq_act_cluster_kernel(const ActParams prm, int slots, int cps, int nsl, int nb_max) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float red[ACT_THREADS / 32];
+    __shared__ float peer_max[8];
+    __shared__ signed char chi[128];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int C = gridDim.x, rank = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
+    const int K = prm.K, m = prm.m, n = prm.n_rot;
+    const int nchunks = K / m, spb = m / 64, NB = P / 4;
+    float * chunks = smem;
+    float * table = chunks + (size_t) slots * m;
+    float * slice = table + P * P;
+    float * outs = slice + P * 64;
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    build_sign_table(table, chi, P, tid, nt);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (t == 0 && rank == 0 && tid == 0 && prm.status != nullptr) *prm.status = 0;
+
+    // ---- Sylvester transform of this CTA's chunks (chunk rank + C*s lands in slot s)
+    const float * xrow = prm.x + (int64_t) t * prm.ldx;
+    {
+        int nloc = 0;
+        for (int ch = rank; ch < nchunks; ch += C) ++nloc;
+        switch (m < 1024 ? m : 1024) {
+            case 64:   cluster_chunks<2>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
+            case 128:  cluster_chunks<4>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
+            case 256:  cluster_chunks<8>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
+            case 512:  cluster_chunks<16>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
+            default:   cluster_chunks<32>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
+        }
+        __syncthreads();
+        for (int ls = 10; (1 << ls) < m; ls += 3) {
+            const int rem = m >> ls;
+            if (rem >= 8) fwht_pass<8>(chunks, nloc * m, ls, tid, nt);
+            else if (rem == 4) fwht_pass<4>(chunks, nloc * m, ls, tid, nt);
+            else fwht_pass<2>(chunks, nloc * m, ls, tid, nt);
+            __syncthreads();
+        }
+    }
+    cluster.sync();
+
+    // ---- Paley, slice by slice
+    const int col = tid & 63, bslot = tid >> 6;            // 4 block slots run side by side
+    const int sub = C >= (K / (64 * P)) ? rank % cps : 0;
+    float tmax = 0.0f;
+    for (int si = 0; si < nsl; ++si) {
+        const int sl = cps > 1 || nsl == 1 ? rank / cps : rank + si * C;
+        const int blk = sl / spb, js = sl - blk * spb;
+        for (int idx = tid; idx < P * 16; idx += nt) {      // the slice's P rows of 64 floats, as float4
+            const int i = idx >> 4, q4 = idx & 15;
+            const int ch = blk * P + i;
+            const float * remote = cluster.map_shared_rank(chunks, ch % C);
+            reinterpret_cast<float4 *>(slice)[idx] = *reinterpret_cast<const float4 *>(remote + (size_t) (ch / C) * m + js * 64 + q4 * 4);
+        }
+        __syncthreads();
+        float colv[P];
+#pragma unroll
+        for (int i = 0; i < P; ++i) colv[i] = slice[i * 64 + col];
+        for (int lb = bslot; lb * cps + sub < NB; lb += 4) {
+            const int ab = lb * cps + sub;
+            float out[4];
+            paley_block4<P>(colv, table, ab * 4, prm.rot_scale, out);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) outs[((si * nb_max + lb) * 4 + k) * 64 + col] = out[k];
+        }
+        __syncthreads();
+    }
+
+    // ---- group ranges: a row of 64 outputs is one activation group (8 lanes x 8 values)
+    int my_nb = 0;
+    for (int ab = sub; ab < NB; ab += cps) ++my_nb;
+    const int words_per_slice = my_nb * 32;                 // 4 rows x 8 words per block
+    for (int si = 0; si < nsl; ++si) {
+        for (int w = tid; w < words_per_slice; w += nt) {
+            const int wi = (si * nb_max * 4) * 8 + w;
+            float lo, hi;
+            group_range(reinterpret_cast<float4 *>(outs)[2 * wi], reinterpret_cast<float4 *>(outs)[2 * wi + 1], 8, prm.clip, lo, hi);
+            tmax = fmaxf(tmax, __fsub_rn(hi, lo));
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+    if ((tid & 31) == 0) red[tid >> 5] = tmax;
+    __syncthreads();
+    if (tid < C) {
+        float v = 0.0f;
+        for (int i = 0; i < nt / 32; ++i) v = fmaxf(v, red[i]);
+        float * remote = cluster.map_shared_rank(peer_max, tid);   // my maximum into slot `rank` of CTA tid
+        remote[rank] = v;
+    }
+    cluster.sync();
+    float R = 0.0f;
+    for (int i = 0; i < C; ++i) R = fmaxf(R, peer_max[i]);
+    if (R == 0.0f) R = 2.0f;
+    const float unit = __fdiv_rn(R, 15.0f * 255.0f);
+    if (rank == 0 && tid == 0) prm.u[t] = unit;
+
+    // ---- codes
+    int8_t * arow = prm.a8 + (int64_t) t * K;
+    int32_t * mrow = prm.msh + (int64_t) t * (K / 64);
+    for (int si = 0; si < nsl; ++si) {
+        const int sl = cps > 1 || nsl == 1 ? rank / cps : rank + si * C;
+        const int blk = sl / spb, js = sl - blk * spb;
+        for (int w = tid; w < words_per_slice; w += nt) {
+            const int row = w >> 3, lb = row >> 2, k = row & 3;
+            const int ab = lb * cps + sub;
+            const int kbase = blk * n + (ab * 4 + k) * m + js * 64;      // first input of this group in the row
+            const int wi = (si * nb_max * 4) * 8 + w;
+            const float4 a = reinterpret_cast<float4 *>(outs)[2 * wi], b = reinterpret_cast<float4 *>(outs)[2 * wi + 1];
+            float lo, hi;
+            group_range(a, b, 8, prm.clip, lo, hi);
+            int mi;
+            const uint2 pk = encode_word(a, b, lo, hi, R, unit, mi);
+            const int off = (w & 7) * 8;
+            *reinterpret_cast<uint32_t *>(arow + kbase + rq_perm64(off)) = pk.x;
+            *reinterpret_cast<uint32_t *>(arow + kbase + rq_perm64(off + 4)) = pk.y;
+            if ((w & 7) == 0) mrow[kbase >> 6] = mi;
+        }
+    }
+}
+
+template <typename Kern, typename... Args>
+cudaError_t launch_ex(Kern kern, dim3 grid, dim3 block, size_t smem, int cluster_x, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = getenv("RQ_NO_PDL") ? 0 : 1;
+    ++na;
+    if (cluster_x > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned) cluster_x;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+constexpr size_t SMEM_LIMIT = 220 * 1024;
+
 template <int P>
 cudaError_t configure() {
-    return cudaFuncSetAttribute(rq_act_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, RQ_MAX_K * 4);
+    cudaError_t e = cudaFuncSetAttribute(rq_act_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
+    if (e != cudaSuccess || P == 1) return e;
+    return cudaFuncSetAttribute(rq_act_cluster_kernel<(P > 1 ? P : 12)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
 }
 
 template <int P>
-cudaError_t launch(const ActParams & prm, int64_t M, size_t smem, cudaStream_t stream) {
+cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -244,8 +514,23 @@ cudaError_t launch(const ActParams & prm, int64_t M, size_t smem, cudaStream_t s
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    rq_act_kernel<P><<<(unsigned) M, ACT_THREADS, smem, stream>>>(prm);
-    return cudaGetLastError();
+    const int K = prm.K;
+    if (P > 1 && prm.a8 != nullptr && prm.rot_out == nullptr && prm.G == 64 && prm.m % 64 == 0 && M <= 32) {
+        // decode widths: a cluster per token
+        const int T = K / (64 * P), NB = P / 4, nchunks = K / prm.m;
+        int C = 8;
+        while (C > 1 && !((C % T == 0 && C / T <= NB) || T % C == 0)) C >>= 1;
+        const int cps = C >= T ? C / T : 1, nsl = C >= T ? 1 : T / C;
+        const int slots = (nchunks + C - 1) / C, nb_max = (NB + cps - 1) / cps;
+        const size_t smem = ((size_t) slots * prm.m + (size_t) P * P + (size_t) P * 64 + (size_t) nsl * nb_max * 4 * 64) * sizeof(float);
+        if (C > 1 && smem <= SMEM_LIMIT) {
+            return launch_ex(rq_act_cluster_kernel<(P > 1 ? P : 12)>, dim3((unsigned) C, (unsigned) M), dim3(ACT_THREADS), smem, C,
+                             stream, prm, slots, cps, nsl, nb_max);
+        }
+    }
+    const size_t smem = ((size_t) K + (P > 1 ? (size_t) P * P : 0)) * sizeof(float);
+    if (smem > SMEM_LIMIT) return cudaErrorInvalidValue;
+    return launch_ex(rq_act_kernel<P>, dim3((unsigned) M), dim3(ACT_THREADS), smem, 1, stream, prm);
 }
 
 }  // namespace
@@ -253,25 +538,36 @@ cudaError_t launch(const ActParams & prm, int64_t M, size_t smem, cudaStream_t s
 // opt every instantiation into the large dynamic shared memory carve-out (done by rq_w4a4_prepare, outside capture)
 cudaError_t rq_configure_act() {
     cudaError_t e;
-    if ((e = configure<0>()) != cudaSuccess) return e;
     if ((e = configure<1>()) != cudaSuccess) return e;
     if ((e = configure<12>()) != cudaSuccess) return e;
     if ((e = configure<20>()) != cudaSuccess) return e;
-    return configure<68>();
+    if ((e = configure<44>()) != cudaSuccess) return e;
+    if ((e = configure<60>()) != cudaSuccess) return e;
+    if ((e = configure<68>()) != cudaSuccess) return e;
+    if ((e = configure<72>()) != cudaSuccess) return e;
+    if ((e = configure<84>()) != cudaSuccess) return e;
+    if ((e = configure<104>()) != cudaSuccess) return e;
+    return configure<108>();
 }
 
 cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,
                           float clip, int G, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,
-                          cudaStream_t stream) {
+                          int32_t * status, cudaStream_t stream) {
     ActParams prm;
     prm.x = x; prm.ldx = ldx; prm.K = (int) K; prm.n_rot = n_rot; prm.p = p; prm.m = m; prm.G = G;
     prm.rot_scale = rot_scale; prm.clip = clip; prm.a8 = a8; prm.msh = msh; prm.u = u; prm.rot_out = rot_out; prm.ldo = ldo;
-    const size_t smem = (size_t) K * sizeof(float);
-    if (n_rot <= 0 || p == 1) return launch<1>(prm, M, smem, stream);
-    switch (p) {
-        case 12: return launch<12>(prm, M, smem, stream);
-        case 20: return launch<20>(prm, M, smem, stream);
-        case 68: return launch<68>(prm, M, smem, stream);
-        default: return launch<0>(prm, M, smem, stream);
+    prm.status = status;
+    if (n_rot <= 0 || p == 1) return launch<1>(prm, M, stream);
+    switch (p) {   // every order the factorisation can return (ggml_rq_hadamard_factor, patch:2419-2430)
+        case 12:  return launch<12>(prm, M, stream);
+        case 20:  return launch<20>(prm, M, stream);
+        case 44:  return launch<44>(prm, M, stream);
+        case 60:  return launch<60>(prm, M, stream);
+        case 68:  return launch<68>(prm, M, stream);
+        case 72:  return launch<72>(prm, M, stream);
+        case 84:  return launch<84>(prm, M, stream);
+        case 104: return launch<104>(prm, M, stream);
+        case 108: return launch<108>(prm, M, stream);
+        default:  return cudaErrorInvalidValue;
     }
 }

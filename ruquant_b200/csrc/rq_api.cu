@@ -99,7 +99,7 @@ static rq_pp_layout rq_pp(int64_t K, int64_t N, int layouts) {
     l.off_sw = 0;
     l.off_wk = rq_align256((uint64_t) N * 4);
     l.off_w4 = l.off_wk + rq_align256((uint64_t) N * (K / 64));
-    l.off_w8 = l.off_w4 + ((layouts & RQ_PREPACK_DECODE) ? rq_align256((uint64_t) N * K / 2) : 0);
+    l.off_w8 = l.off_w4 + ((layouts & RQ_PREPACK_DECODE) ? rq_align256((uint64_t) ((N + 15) / 16) * 16 * K / 2) : 0);
     l.bytes = l.off_w8 + ((layouts & RQ_PREPACK_PREFILL) ? rq_align256((uint64_t) N * K) : 0);
     return l;
 }
@@ -204,7 +204,7 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_rotate(const float
     if (n_rot <= 0 || K % n_rot != 0 || !rq_hadamard_factor(n_rot, &p, &m)) return RQ_ERR_ROTATION;
     const float scale = 1.0f / sqrtf((float) n_rot);
     RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, 1.0f, 64, nullptr, nullptr, nullptr, out_dev, ldo,
-                          (cudaStream_t) stream));
+                          nullptr, (cudaStream_t) stream));
     return RQ_OK;
 }
 
@@ -226,10 +226,9 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize(const flo
         return RQ_ERR_ROTATION;
     }
     uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
-    RQ_CUDA(cudaMemsetAsync(ws + l.off_status, 0, 4, (cudaStream_t) stream));
     RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, clip, act_group, reinterpret_cast<int8_t *>(ws + l.off_a8),
                           reinterpret_cast<int32_t *>(ws + l.off_msh), reinterpret_cast<float *>(ws + l.off_u), nullptr, 0,
-                          (cudaStream_t) stream));
+                          reinterpret_cast<int32_t *>(ws + l.off_status), (cudaStream_t) stream));
     return RQ_OK;
 }
 
@@ -254,12 +253,12 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(
     else if (path == RQ_PATH_TC) { if (!has_pre) return RQ_ERR_ARG; tc = true; }
     else if (path == RQ_PATH_AUTO) tc = has_pre && (M > 16 || !has_dec);
     else return RQ_ERR_ARG;
+    int32_t * status = reinterpret_cast<int32_t *>(const_cast<uint8_t *>(ws) + l.off_status);
     if (tc) {
-        int32_t * status = reinterpret_cast<int32_t *>(const_cast<uint8_t *>(ws) + l.off_status);
         RQ_CUDA(rq_launch_gemm_tc(w->tmap_w8, sw, w->wk_mode, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
     } else {
         const int8_t * wk = w->wk_mode ? reinterpret_cast<const int8_t *>(pp + w->off_wk) : nullptr;
-        RQ_CUDA(rq_launch_gemv(pp + w->off_w4, sw, wk, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, stream));
+        RQ_CUDA(rq_launch_gemv(pp + w->off_w4, sw, wk, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
     }
     return RQ_OK;
 }

@@ -24,11 +24,17 @@ __host__ __device__ inline int rq_wmult(int32_t sum, int g) {
     return 1;
 }
 
-// The activation multiplier m_g (1..255) is stored pre-shifted so that one signed high multiply folds a group:
-// the contraction delivers D = 128 * S (weights as 16*c, activations as 8*(q-z)), and
-// mulhi(D, m << 21) = floor(128*S*m*2^21 / 2^32) = (m*S) >> 4, the reference's arithmetic shift
-// (RQ_TERM_SHIFT, patch:39 and ggml_vec_dot_w4a4_a4, patch:173).
-#define RQ_MSH_SHIFT 21
+// The contraction delivers D = 128 * S_g (weights as 16*c, activations as 8*(q-z)); the reference's term
+// (m_g * S_g) >> 4 (RQ_TERM_SHIFT, patch:39 and ggml_vec_dot_w4a4_a4, patch:173) is then (m_g * D) >> 11, exact,
+// and m_g * D stays below 2^31 for every group width (255 * 128 * 120 * 256 < 2^30).
+#define RQ_FOLD_SHIFT 11
+// Inside every run of 64 inputs both int8 operands (activations a8, tensor-core weights w8) are stored permuted:
+// the 4 inputs 16*i + 4*t .. +3 (i, t in 0..3) sit at bytes 16*t + 4*i .. +3, so that the 16 bytes at 16*t are the
+// B fragment (k = {0,16,32,48} + 4*t .. +3) of the two m16n8k32 MMAs that cover the run.  A dot product over the run
+// does not care about the order as long as both operands agree.
+__host__ __device__ inline int rq_perm64(int k4) {   // k4: offset of a 4-input piece inside the run (multiple of 4)
+    return ((k4 & 15) >> 2) * 16 + (k4 >> 4) * 4;
+}
 #define RQ_ACT_SCALE 8     // activations are stored as 8*(q - z), |.| <= 120
 #define RQ_W_SCALE   16    // weights with multiplier 1 are stored as 16*c, in [-128, 112]
 
@@ -50,13 +56,13 @@ static inline rq_ws_layout rq_ws(int64_t K, int64_t M) {
 // Launchers (one per .cu file).  All enqueue on `stream` and return a cudaError_t.
 cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,
                           float clip, int G, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,
-                          cudaStream_t stream);
+                          int32_t * status, cudaStream_t stream);
 cudaError_t rq_launch_prepack(const rq_block * blocks, int64_t K, int64_t N, float * sw, uint8_t * w4, int8_t * w8,
                               int8_t * wk, int wk_mode, cudaStream_t stream);
 cudaError_t rq_launch_scan_wk(const rq_block * blocks, int64_t n_blocks, int32_t * flag, cudaStream_t stream);
 cudaError_t rq_launch_gemv(const uint8_t * w4, const float * sw, const int8_t * wk, int64_t K, int64_t N,
                            const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
-                           float * y, int64_t ldy, cudaStream_t stream);
+                           float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mode, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream);

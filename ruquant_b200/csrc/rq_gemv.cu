@@ -1,201 +1,338 @@
 // Decode-width contraction (M <= 16 tokens per pass): an HBM-bound GEMV over the int4 decode stream.
 //
-// A lane owns 32 consecutive inputs of a row per step (one 128-bit load of the stream), a warp 1024; G/32
-// neighbouring lanes make up one activation group and combine their partial sums with shuffles, so every group of
-// every (row, token) pair is folded on its own, as the reference's dot product does
-// (ggml_vec_dot_w4a4_a4, ggml/src/ggml-cpu/quants.c in patches/llama.cpp-ruquant.patch:148-177):
+// The stream is stored in the order the warp consumes it (rq_prepack.cu): for every tile of 16 weight rows and every
+// run of 64 inputs, 512 contiguous bytes = one 128-bit load per lane, whose four words unpack (two logic ops each)
+// into the eight int8 A-fragment registers of two m16n8k32 integer MMAs.  The MMAs do the multiply-accumulate for
+// up to 8 tokens at once, so the instruction count per byte of weights does not grow with M and the kernel stays
+// bandwidth-bound from M = 1 to 16.  Every activation group of every (row, token) pair is folded on its own, as
+// the reference's dot product does (ggml_vec_dot_w4a4_a4, ggml/src/ggml-cpu/quants.c in
+// patches/llama.cpp-ruquant.patch:148-177):
 //     total += (k * m_g * S_g) >> 4,   S_g = sum c * (q - z_g)       (int32, arithmetic shift)
 //     y = ((float(total) * 16) * u) * s_w                             (three separate fp32 multiplies)
-// Weights arrive as int8 16*c (two logic ops per word, see rq_prepack.cu), activations as int8 8*(q - z), so a
-// group's dp4a sum is 128*S_g and the shift by 7 that recovers S_g is exact.
+// Weights arrive as int8 16*c, activations as int8 8*(q - z), so the MMA delivers 128*S_g and the fold is
+// (m_g * 128*S_g) >> 11, exact.  The stream reaches shared memory through bulk asynchronous copies issued by a
+// producer warp (deep, register-free prefetch: HBM on this part needs > 100 KB in flight per SM); the consumer warps
+// of a CTA split K (integer sums are exact in any order) and combine through shared memory.  The kernel is launched
+// with programmatic stream serialization: it lets its successor start at once and fills its ring before waiting for
+// the quantizer that precedes it.
+#include <stdlib.h>
+
 #include "rq_common.cuh"
 
 namespace {
 
-constexpr int GEMV_WARPS = 4;
 
-__device__ __forceinline__ uint4 ld_stream(const void * p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+__device__ __forceinline__ void mma_s8(int (&d)[4], const int (&a)[4], int b0, int b1, const int (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
 struct GemvParams {
-    const uint8_t * w4;
+    const uint4 * w4t;      // [tiles][K/64][32 lanes] x 16 B
     const float * sw;
-    const int8_t * wk;
-    const int8_t * a8;
-    const int32_t * msh;
+    const int8_t * wk;      // [N][K/64] or null
+    const int8_t * a8;      // [M][K]  8*(q - z)
+    const int32_t * msh;    // [M][K/G]  m_g
     const float * u;
     float * y;
     int64_t ldy;
+    int32_t * status;       // set to 1 when a bounded wait expires
     int K, N, M, G;
 };
 
-// TT tokens per pass, R rows per warp, KS warps of the CTA splitting K (1 or GEMV_WARPS)
-template <int TT, int R, int KS, bool HAS_K>
-__global__ void __launch_bounds__(GEMV_WARPS * 32) rq_gemv_kernel(const GemvParams prm) {
-    __shared__ int32_t part[GEMV_WARPS][R][TT];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int K = prm.K, N = prm.N, M = prm.M;
-    const int units = K >> 5;                 // 32-input lane units per row
-    const int n_it = (units + 31) >> 5;
-    const int lpg = prm.G >> 5;               // lanes per activation group: 2, 4 or 8
-    const int ngrp = K / prm.G;
-    const int rows_per_cta = KS == 1 ? R * GEMV_WARPS : R;
-    const int row0 = blockIdx.x * rows_per_cta + (KS == 1 ? warp * R : 0);
-    const int ks = KS == 1 ? 0 : warp;
+constexpr int CH_STEPS = 4;                 // 64-input steps per chunk of the stream
+constexpr int CH_BYTES = CH_STEPS * 512;    // 2 KB: one bulk copy, owned by one consumer warp
+constexpr int STAGES = 32;                  // 64 KB ring per CTA
+constexpr int CONSUMERS = 8;                // consumer warps; warp CONSUMERS is the producer
+constexpr long long WAIT_CYCLES = 2000000000ll;
 
-    int32_t tot[R][TT];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int t = 0; t < TT; ++t) tot[r][t] = 0;
-
-    const size_t row_bytes = (size_t) K >> 1;
-    uint4 wv[R];
-    {
-        const int unit = ks * 32 + lane;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            wv[r] = make_uint4(0u, 0u, 0u, 0u);
-            if (ks < n_it && unit < units && row0 + r < N) wv[r] = ld_stream(prm.w4 + (size_t) (row0 + r) * row_bytes + (size_t) unit * 16);
-        }
-    }
-    for (int it = ks; it < n_it; it += KS) {
-        const int unit = it * 32 + lane;
-        const bool active = unit < units;
-        uint4 wn[R];
-        {
-            const int nu = unit + KS * 32;
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                wn[r] = make_uint4(0u, 0u, 0u, 0u);
-                if (it + KS < n_it && nu < units && row0 + r < N) wn[r] = ld_stream(prm.w4 + (size_t) (row0 + r) * row_bytes + (size_t) nu * 16);
-            }
-        }
-        const int g = active ? unit / lpg : 0;
-        int kk[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            kk[r] = 1;
-            if (HAS_K) kk[r] = (active && row0 + r < N) ? (int) prm.wk[(size_t) (row0 + r) * (K >> 6) + (unit >> 1)] : 1;
-        }
-        // the int8 views of this lane's 32 codes: lo[j] = 16*(c[8j..8j+3]), hi[j] = 16*(c[8j+4..8j+7])
-        int lo[R][4], hi[R][4];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const uint32_t w[4] = { wv[r].x, wv[r].y, wv[r].z, wv[r].w };
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                lo[r][j] = (int) ((w[j] << 4) & 0xF0F0F0F0u);
-                hi[r][j] = (int) (w[j] & 0xF0F0F0F0u);
-            }
-        }
-#pragma unroll
-        for (int t = 0; t < TT; ++t) {
-            uint4 a0 = make_uint4(0u, 0u, 0u, 0u), a1 = a0;
-            int mval = 0;
-            if (active && t < M) {
-                const uint4 * ap = reinterpret_cast<const uint4 *>(prm.a8 + (size_t) t * K + (size_t) unit * 32);
-                a0 = __ldg(ap);
-                a1 = __ldg(ap + 1);
-                mval = __ldg(prm.msh + (size_t) t * ngrp + g) >> RQ_MSH_SHIFT;
-            }
-            const int aw[8] = { (int) a0.x, (int) a0.y, (int) a0.z, (int) a0.w, (int) a1.x, (int) a1.y, (int) a1.z, (int) a1.w };
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                int s = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    s = __dp4a(lo[r][j], aw[2 * j], s);
-                    s = __dp4a(hi[r][j], aw[2 * j + 1], s);
-                }
-                for (int o = 1; o < lpg; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if ((lane & (lpg - 1)) == 0) tot[r][t] += (kk[r] * mval * (s >> 7)) >> 4;
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) wv[r] = wn[r];
-    }
-
-    // integer sums are exact in any order: lanes first, then (KS > 1) the warps that split K
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int t = 0; t < TT; ++t) {
-            int v = tot[r][t];
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            tot[r][t] = v;
-        }
-    if (KS > 1) {
-        if (lane == 0) {
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int t = 0; t < TT; ++t) part[warp][r][t] = tot[r][t];
-        }
-        __syncthreads();
-        if (warp != 0) return;
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int t = 0; t < TT; ++t) {
-                int v = 0;
-                for (int w = 0; w < GEMV_WARPS; ++w) v += part[w][r][t];
-                tot[r][t] = v;
-            }
-    }
-    // epilogue: lane (r, t) pairs spread over the warp
-    for (int i = lane; i < R * TT; i += 32) {
-        const int r = i / TT, t = i - r * TT;
-        int v = 0;
-#pragma unroll
-        for (int rr = 0; rr < R; ++rr)
-#pragma unroll
-            for (int tt = 0; tt < TT; ++tt) if (rr == r && tt == t) v = tot[rr][tt];
-        if (row0 + r < N && t < M) {
-            const float f = __fmul_rn(__fmul_rn(__fmul_rn((float) v, 16.0f), __ldg(prm.u + t)), __ldg(prm.sw + row0 + r));
-            prm.y[(size_t) t * prm.ldy + row0 + r] = f;
+__device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false when the barrier did not flip in about a second or another warp already gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int * abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; return false; }
         }
     }
 }
 
-template <int TT, int R>
-cudaError_t launch_tt(const GemvParams & prm, bool has_k, cudaStream_t stream) {
-    // few rows: let the CTA's warps split K so that enough warps are in flight to cover HBM latency
-    const bool split = (int64_t) prm.N / R < 148 * 16;
-    const int rows_per_cta = split ? R : R * GEMV_WARPS;
-    const unsigned grid = (unsigned) ((prm.N + rows_per_cta - 1) / rows_per_cta);
-    if (split) {
-        if (has_k) rq_gemv_kernel<TT, R, GEMV_WARPS, true><<<grid, GEMV_WARPS * 32, 0, stream>>>(prm);
-        else       rq_gemv_kernel<TT, R, GEMV_WARPS, false><<<grid, GEMV_WARPS * 32, 0, stream>>>(prm);
-    } else {
-        if (has_k) rq_gemv_kernel<TT, R, 1, true><<<grid, GEMV_WARPS * 32, 0, stream>>>(prm);
-        else       rq_gemv_kernel<TT, R, 1, false><<<grid, GEMV_WARPS * 32, 0, stream>>>(prm);
+// Persistent CTAs, three per SM, each walking tiles of 16 weight rows (tile = blockIdx.x, += gridDim.x).  The producer
+// warp streams the tiles' K/64 * 512 bytes back to back into a shared-memory ring with bulk copies (it starts at once:
+// the weights do not depend on the preceding kernel, and it never drains between tiles); the consumer warps take the
+// chunks of that stream round-robin, so 64 KB per CTA stay in flight or resident from the first cycle to the last.
+// NT: token tiles of 8 (1 or 2).  GS: 64-input steps per activation group (1, 2, 4).  HAS_K: weight multipliers.
+// ONE: M == 1 (only token 0 is folded and stored).
+template <int NT, int GS, bool HAS_K, bool ONE>
+__global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const GemvParams prm) {
+    extern __shared__ __align__(128) uint8_t dyn[];
+    __shared__ uint64_t full[STAGES], empty[STAGES];
+    __shared__ int abort_word;
+    uint8_t * ring = dyn;
+    int * part = reinterpret_cast<int *>(dyn + STAGES * CH_BYTES);      // [2][CONSUMERS][32][4 * NT]
+    volatile int * abort_flag = &abort_word;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int K = prm.K, M = prm.M;
+    const int ng64 = K >> 6, n_ag = ng64 / GS, nchunks = ng64 / CH_STEPS;
+    const int tiles = (prm.N + 15) / 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&empty[s])) : "memory");
+        }
+        abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    return cudaGetLastError();
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == CONSUMERS) {
+        // ---- producer: bulk copies of 2 KB, gated only by ring space
+        if (lane == 0) {
+            int issued = 0;       // chunks of this CTA's stream, all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const uint8_t * src = reinterpret_cast<const uint8_t *>(prm.w4t) + (size_t) tile * ng64 * 512;
+                for (int c = 0; c < nchunks; ++c) {
+                    const int s = issued % STAGES;
+                    if (!mbar_wait(smem_u32(&empty[s]), ((issued / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full[s]);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(CH_BYTES) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 :: "r"(smem_u32(ring + (size_t) s * CH_BYTES)), "l"(src + (size_t) c * CH_BYTES), "r"(CH_BYTES), "r"(bar) : "memory");
+                    ++issued;
+                }
+            }
+            if (*abort_flag) {   // let every copy that was issued land before the CTA's shared memory goes away
+                for (int c = issued > STAGES ? issued - STAGES : 0; c < issued; ++c) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&full[c % STAGES]), (c / STAGES) & 1) && clock64() - t0 < WAIT_CYCLES) { }
+                }
+                if (prm.status != nullptr) atomicExch(prm.status, 1);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers.  Everything below reads what the preceding kernel (the quantizer) wrote.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // B fragments: token gid (+8 for the second tile); the quantizer stores each run of 64 inputs so that the 16
+    // bytes at offset tig*16 are inputs {0,16,32,48} + tig*4 .. +3: b0, b1 of both MMAs in one 128-bit load
+    const uint4 * ap[NT];
+    bool tok_ok[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        tok_ok[t] = gid + 8 * t < M;
+        ap[t] = reinterpret_cast<const uint4 *>(prm.a8 + (size_t) (tok_ok[t] ? gid + 8 * t : 0) * K) + tig;
+    }
+    const int32_t * mp[NT][2];
+    bool m_ok[NT][2];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int tok = 8 * t + 2 * tig + c;
+            m_ok[t][c] = tok < M;
+            mp[t][c] = prm.msh + (size_t) (m_ok[t][c] ? tok : 0) * n_ag;
+        }
+
+    int it = 0;                                    // tiles done by this CTA
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+        const int row_lo = tile * 16 + gid, row_hi = row_lo + 8;
+        const int8_t * kp_lo = nullptr, * kp_hi = nullptr;
+        if (HAS_K) {
+            kp_lo = prm.wk + (size_t) (row_lo < prm.N ? row_lo : 0) * ng64;
+            kp_hi = prm.wk + (size_t) (row_hi < prm.N ? row_hi : 0) * ng64;
+        }
+        int tot[NT][4];
+        int acc[NT][4];
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { tot[t][i] = 0; acc[t][i] = 0; }
+
+        // chunk gc of the CTA's stream (all tiles) belongs to consumer warp gc % CONSUMERS
+        const int gc0 = it * nchunks;
+        bool ok = true;
+        for (int c = ((warp - gc0) % CONSUMERS + CONSUMERS) % CONSUMERS; c < nchunks; c += CONSUMERS) {
+            const int gc = gc0 + c, s = gc % STAGES;
+            // the MMAs below are warp-collective: leave the loop together or not at all
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full[s]), (gc / STAGES) & 1, abort_flag))) { ok = false; break; }
+            const uint4 * sp_ = reinterpret_cast<const uint4 *>(ring + (size_t) s * CH_BYTES) + lane;
+            // The integer MMA of this part has a long latency: issue the MMAs of SP steps (two per step, on
+            // independent zero-initialised accumulators) before touching any result.
+            constexpr int SP = NT == 1 ? 4 : 2;
+#pragma unroll
+            for (int h = 0; h < CH_STEPS; h += SP) {
+                int pa[SP][2][NT][4];
+#pragma unroll
+                for (int sp = 0; sp < SP; ++sp) {
+                    const int j = c * CH_STEPS + h + sp;          // 64-input step of the tile
+                    const uint4 wv = sp_[(h + sp) * 32];
+                    uint4 b[NT];
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) b[t] = tok_ok[t] ? __ldg(ap[t] + j * 4) : make_uint4(0u, 0u, 0u, 0u);
+                    // words 0,1 -> first 32 inputs (a0..a3), words 2,3 -> second 32 inputs
+                    int a0[4], a1[4];
+                    a0[0] = (int) ((wv.x << 4) & 0xF0F0F0F0u); a0[1] = (int) (wv.x & 0xF0F0F0F0u);
+                    a0[2] = (int) ((wv.y << 4) & 0xF0F0F0F0u); a0[3] = (int) (wv.y & 0xF0F0F0F0u);
+                    a1[0] = (int) ((wv.z << 4) & 0xF0F0F0F0u); a1[1] = (int) (wv.z & 0xF0F0F0F0u);
+                    a1[2] = (int) ((wv.w << 4) & 0xF0F0F0F0u); a1[3] = (int) (wv.w & 0xF0F0F0F0u);
+                    const int zero[4] = { 0, 0, 0, 0 };
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        mma_s8(pa[sp][0][t], a0, (int) b[t].x, (int) b[t].y, zero);
+                        mma_s8(pa[sp][1][t], a1, (int) b[t].z, (int) b[t].w, zero);
+                    }
+                }
+#pragma unroll
+                for (int sp = 0; sp < SP; ++sp) {
+                    const int st = h + sp, j = c * CH_STEPS + st;
+#pragma unroll
+                    for (int t = 0; t < NT; ++t)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[t][i] += pa[sp][0][t][i] + pa[sp][1][t][i];
+                    if ((st % GS) == GS - 1) {
+                        const int ag = j / GS;
+                        int klo = 1, khi = 1;
+                        if (HAS_K) { klo = kp_lo[j]; khi = kp_hi[j]; }
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) {
+                            const int m0 = m_ok[t][0] ? __ldg(mp[t][0] + ag) : 0;
+                            const int m1 = (!ONE && m_ok[t][1]) ? __ldg(mp[t][1] + ag) : 0;
+                            if (HAS_K) {
+                                tot[t][0] += (klo * m0 * (acc[t][0] >> 7)) >> 4;
+                                tot[t][2] += (khi * m0 * (acc[t][2] >> 7)) >> 4;
+                                if (!ONE) {
+                                    tot[t][1] += (klo * m1 * (acc[t][1] >> 7)) >> 4;
+                                    tot[t][3] += (khi * m1 * (acc[t][3] >> 7)) >> 4;
+                                }
+                            } else {
+                                tot[t][0] += (m0 * acc[t][0]) >> RQ_FOLD_SHIFT;
+                                tot[t][2] += (m0 * acc[t][2]) >> RQ_FOLD_SHIFT;
+                                if (!ONE) {
+                                    tot[t][1] += (m1 * acc[t][1]) >> RQ_FOLD_SHIFT;
+                                    tot[t][3] += (m1 * acc[t][3]) >> RQ_FOLD_SHIFT;
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&empty[s])) : "memory");
+        }
+
+        // combine the consumer warps (integer sums are exact in any order); partials are double-buffered by tile
+        // parity, and the warp that reduces and stores rotates from tile to tile
+        int * pt = part + (it & 1) * (CONSUMERS * 32 * 4 * NT);
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pt[(warp * 32 + lane) * 4 * NT + t * 4 + i] = tot[t][i];
+        asm volatile("bar.sync 1, %0;" :: "n"(CONSUMERS * 32) : "memory");
+        if (!ok || *abort_flag) return;
+        if (warp != it % CONSUMERS) continue;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int v = 0;
+                for (int w = 0; w < CONSUMERS; ++w) v += pt[(w * 32 + lane) * 4 * NT + t * 4 + i];
+                tot[t][i] = v;
+            }
+        const float s_lo = row_lo < prm.N ? __ldg(prm.sw + row_lo) : 0.0f;
+        const float s_hi = row_hi < prm.N ? __ldg(prm.sw + row_hi) : 0.0f;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int tok = 8 * t + 2 * tig + c;
+                if (tok < M) {
+                    const float ut = __ldg(prm.u + tok);
+                    if (row_lo < prm.N) prm.y[(size_t) tok * prm.ldy + row_lo] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][c], 16.0f), ut), s_lo);
+                    if (row_hi < prm.N) prm.y[(size_t) tok * prm.ldy + row_hi] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][2 + c], 16.0f), ut), s_hi);
+                }
+            }
+        }
+    }
+}
+
+template <int NT, int GS, bool HAS_K, bool ONE>
+cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
+    static bool configured[64] = {};
+    const size_t smem = (size_t) STAGES * CH_BYTES + 2 * (size_t) CONSUMERS * 32 * 4 * NT * sizeof(int);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(rq_gemv_mma_kernel<NT, GS, HAS_K, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = (prm.N + 15) / 16;
+    cfg.gridDim = dim3((unsigned) (tiles < 3 * sms ? tiles : 3 * sms));
+    cfg.blockDim = dim3((CONSUMERS + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = getenv("RQ_NO_PDL") ? 0 : 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE>, prm);
+}
+
+template <int NT, int GS, bool HAS_K>
+cudaError_t launch(const GemvParams & prm, cudaStream_t stream) {
+    if (NT == 1 && prm.M == 1) return launch_one<1, GS, HAS_K, true>(prm, stream);
+    return launch_one<NT, GS, HAS_K, false>(prm, stream);
+}
+
+template <int NT>
+cudaError_t launch_nt(const GemvParams & prm, bool has_k, cudaStream_t stream) {
+    const int gs = prm.G / 64;
+    if (has_k) {
+        if (gs == 1) return launch<NT, 1, true>(prm, stream);
+        if (gs == 2) return launch<NT, 2, true>(prm, stream);
+        return launch<NT, 4, true>(prm, stream);
+    }
+    if (gs == 1) return launch<NT, 1, false>(prm, stream);
+    if (gs == 2) return launch<NT, 2, false>(prm, stream);
+    return launch<NT, 4, false>(prm, stream);
 }
 
 }  // namespace
 
 cudaError_t rq_launch_gemv(const uint8_t * w4, const float * sw, const int8_t * wk, int64_t K, int64_t N,
                            const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
-                           float * y, int64_t ldy, cudaStream_t stream) {
+                           float * y, int64_t ldy, int32_t * status, cudaStream_t stream) {
     // wider inputs go through in passes of 16 tokens, each re-reading the stream
     for (int64_t t0 = 0; t0 < M; t0 += 16) {
         const int mt = (int) (M - t0 < 16 ? M - t0 : 16);
         GemvParams prm;
-        prm.w4 = w4; prm.sw = sw; prm.wk = wk; prm.K = (int) K; prm.N = (int) N; prm.M = mt; prm.G = G;
-        prm.a8 = a8 + t0 * K; prm.msh = msh + t0 * (K / G); prm.u = u + t0; prm.y = y + t0 * ldy; prm.ldy = ldy;
-        cudaError_t e;
-        const bool has_k = wk != nullptr;
-        if (mt == 1) e = launch_tt<1, 4>(prm, has_k, stream);
-        else if (mt == 2) e = launch_tt<2, 4>(prm, has_k, stream);
-        else if (mt <= 4) e = launch_tt<4, 4>(prm, has_k, stream);
-        else if (mt <= 8) e = launch_tt<8, 2>(prm, has_k, stream);
-        else e = launch_tt<16, 2>(prm, has_k, stream);
+        prm.w4t = reinterpret_cast<const uint4 *>(w4); prm.sw = sw; prm.wk = wk;
+        prm.K = (int) K; prm.N = (int) N; prm.M = mt; prm.G = G;
+        prm.a8 = a8 + t0 * K; prm.msh = msh + t0 * (K / G); prm.u = u + t0; prm.y = y + t0 * ldy; prm.ldy = ldy; prm.status = status;
+        const cudaError_t e = mt <= 8 ? launch_nt<1>(prm, wk != nullptr, stream) : launch_nt<2>(prm, wk != nullptr, stream);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
