@@ -3,7 +3,8 @@
 
 Workload (config.workload): the 64-layer 27B-shaped decoder linear stack in W4A4H -- per layer q 5120->6144,
 k 5120->1024, v 5120->1024, o 6144->5120, gate 5120->17408, up 5120->17408, down 17408->5120 -- run as M = 1 decode.
-A step is one pass over all 448 matmuls, every matmul on its own fp32 N(0,1) activation; weights are synthetic
+A step is one pass over all 448 matmuls; per layer four fp32 N(0,1) activations as in the decoder (q/k/v share one,
+gate/up share one, o and down have their own) and matmuls that share an activation are one call; weights are synthetic
 N(0, 0.02) rows rotated and quantized to W4A4H on the GPU (ruquant_b200.synth); 12.27 GB of weight blocks, so every
 step streams far more than the 126 MB L2.  `value` is algorithmic GB/s: sum over matmuls of
 N*(K/256)*144 + 4*M*K + 4*M*N bytes, divided by the step time, inputs resident in HBM.  `e2e` is the same pass
@@ -28,6 +29,8 @@ if ROOT not in sys.path:
 
 LAYER = [("q", 5120, 6144), ("k", 5120, 1024), ("v", 5120, 1024), ("o", 6144, 5120), ("gate", 5120, 17408),
          ("up", 5120, 17408), ("down", 17408, 5120)]
+LAYER_DIMS = {name: (K, N) for name, K, N in LAYER}
+GROUPS = [("q", "k", "v"), ("o",), ("gate", "up"), ("down",)]      # matmuls that share an activation
 PREFILL = ("gate_up", 5120, 17408, 4096)
 METRIC = "W4A4H decode GB/s @M=1 over the 64-layer 27B-shaped linear stack (prefill TOPS @M=4096 under 'prefill')"
 
@@ -159,34 +162,48 @@ def run_ours(args):
     hbm_peak, _, peak_kind = measured_peaks()
     L = args.layers
 
-    # ---- the stack: rank r holds rows [r*N/g, (r+1)*N/g) of every tensor
-    mats = []          # (K, N_total, N_local, Weight, x_dev, y_local, y_full, workspace)
+    # ---- the stack: rank r holds rows [r*N/g, (r+1)*N/g) of every tensor.  Per layer four activations, as in the
+    # decoder: attention input -> q, k, v; attention output -> o; MLP input -> gate, up; MLP hidden -> down.  Weights
+    # that share an activation go through one call (one rotate+quantize, one GEMV launch over all their row tiles),
+    # the reference's fused launch for such matmuls (ggml_cuda_try_fuse).
+    groups = []        # (K, x_dev, workspace, [(N_total, N_local, Weight, y_local, y_full)])
+    mats = []          # flat list of (K, N_total) for the byte count
     for layer in range(L):
-        for ti, (name, K, N) in enumerate(LAYER):
-            nl = N // world
-            blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=100000 * layer + 100 * ti + rank, device=dev)
-            w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_DECODE)
-            if layer > 0:
-                w.blocks = None      # the kernels read only the prepacked stream; layer 0's blocks feed the CPU baseline
-            del blocks
+        for gi, names in enumerate(GROUPS):
+            K = LAYER_DIMS[names[0]][0]
             g = torch.Generator(device=dev)
-            g.manual_seed(7_000_000 + 10 * layer + ti)
+            g.manual_seed(7_000_000 + 10 * layer + gi)
             x = torch.randn((1, K), generator=g, device=dev, dtype=torch.float32)
-            y_full = torch.empty((1, N), device=dev, dtype=torch.float32)
-            y_loc = y_full if world == 1 else torch.empty((1, nl), device=dev, dtype=torch.float32)
-            mats.append((K, N, nl, w, x, y_loc, y_full, rq.new_workspace(K, 1, dev)))
+            members = []
+            for name in names:
+                _, N = LAYER_DIMS[name]
+                ti = [n for n, _k, _n in LAYER].index(name)
+                nl = N // world
+                blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=100000 * layer + 100 * ti + rank, device=dev)
+                w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_DECODE)
+                w.blocks = None      # the kernels read only the prepacked stream
+                del blocks
+                y_full = torch.empty((1, N), device=dev, dtype=torch.float32)
+                y_loc = y_full if world == 1 else torch.empty((1, nl), device=dev, dtype=torch.float32)
+                members.append((N, nl, w, y_loc, y_full))
+                mats.append((K, N))
+            groups.append((K, x, rq.new_workspace(K, 1, dev), members))
     torch.cuda.synchronize()
-    total_bytes = sum(algorithmic_bytes(K, N, 1) for (K, N, *_r) in mats)
+    # algorithmic bytes: every weight block and every output once, every activation once per group that shares it
+    total_bytes = sum(N * (K // 256) * 144 + 4 * N for (K, N) in mats) + sum(4 * K for (K, *_r) in groups)
     stream = torch.cuda.Stream(device=dev)
 
     def enqueue_pass(quantize=True):
-        for K, N, nl, w, x, y_loc, y_full, ws in mats:
+        for K, x, ws, members in groups:
+            weights = [m[2] for m in members]
+            outs = [m[3] for m in members]
             if quantize:
-                rq.mul_mat(w, x, out=y_loc, clip=1.0, act_group=64, workspace=ws, stream=stream)
+                rq.mul_mat(weights, x, out=outs, clip=1.0, act_group=64, workspace=ws, stream=stream)
             else:
-                rq.mul_mat_quantized(w, 1, ws, out=y_loc, act_group=64, stream=stream)
+                rq.mul_mat_quantized(weights, 1, ws, out=outs, act_group=64, stream=stream)
             if world > 1:
-                dist.all_gather_into_tensor(y_full.view(-1), y_loc.view(-1))
+                for N, nl, w, y_loc, y_full in members:
+                    dist.all_gather_into_tensor(y_full.view(-1), y_loc.view(-1))
 
     def capture(fn):
         g = torch.cuda.CUDAGraph()
@@ -235,21 +252,22 @@ def run_ours(args):
         achieved = total_bytes / (ms_gemv * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "rq_gemv_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                     "frac": achieved / hbm_peak, "peak_kind": "of " + peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
-                    "avg_launch_us": ms_gemv * 1e3 / len(mats), "launches_per_step": len(mats),
-                    "algorithmic_bytes_per_launch": total_bytes / len(mats), "traffic": None}
+                    "avg_launch_us": ms_gemv * 1e3 / len(groups), "launches_per_step": len(groups),
+                    "algorithmic_bytes_per_launch": total_bytes / len(groups), "traffic": None}
 
     # ---- end to end through the C ABI with host buffers
-    x_host = [torch.randn((1, K), dtype=torch.float32).pin_memory() for (K, *_r) in mats]
-    y_host = [torch.empty((1, N), dtype=torch.float32).pin_memory() for (_K, N, *_r) in mats]
+    x_host = [torch.randn((1, K), dtype=torch.float32).pin_memory() for (K, *_r) in groups]
+    y_host = [[torch.empty((1, m[0]), dtype=torch.float32).pin_memory() for m in members] for (_K, _x, _ws, members) in groups]
     h2d = sum(x.numel() * 4 for x in x_host)
-    d2h = sum(y.numel() * 4 for y in y_host)
+    d2h = sum(y.numel() * 4 for ys in y_host for y in ys)
 
     def e2e_step():
-        for (K, N, nl, w, x, y_loc, y_full, ws), xh in zip(mats, x_host):
+        for (K, x, ws, members), xh in zip(groups, x_host):
             x.copy_(xh, non_blocking=True)
         g_pass.replay()
-        for (K, N, nl, w, x, y_loc, y_full, ws), yh in zip(mats, y_host):
-            yh.copy_(y_full, non_blocking=True)
+        for (K, x, ws, members), yhs in zip(groups, y_host):
+            for m, yh in zip(members, yhs):
+                yh.copy_(m[4], non_blocking=True)
 
     ms_e2e = timed(e2e_step, args.steps, args.warmup)
     e2e = {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -301,13 +319,14 @@ def run_ours(args):
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int4 x int4 -> int32, fp32 epilogue", "data": "synthetic",
                 "config": {"workload": "27B-shaped %d-layer W4A4H linear stack, M=1 decode, 7 matmuls per layer" % L,
-                           "weights_gb": sum(N * (K // 256) * 144 for (K, N, *_r) in mats) / 1e9,
+                           "weights_gb": sum(N * (K // 256) * 144 for (K, N) in mats) / 1e9,
+                           "activation_sharing": "q,k,v | o | gate,up | down: one rotate+quantize and one GEMV launch per group",
                            "l2": "inputs larger than L2 (weights streamed once per step)",
                            "parallelism": "N-sharded x%d, NCCL all-gather per matmul" % world if world > 1 else "single GPU",
                            "cuda_graph": True},
                 "frac_of_hbm_peak": value / (hbm_peak * world), "peak_kind": "of " + peak_kind,
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "prefill": prefill, "clocks": clocks,
-                "gpu_launches": 2 * len(mats) * args.steps}
+                "gpu_launches": 2 * len(groups) * args.steps}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

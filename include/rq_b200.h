@@ -121,6 +121,12 @@ int rq_w4a4_mul_mat(const rq_weight_desc * const * w, int n_w, const float * x_d
 int rq_w4a4_mul_mat_quantized(const rq_weight_desc * w, int64_t M, float * y_dev, int64_t ldy, int act_group, int path,
                               void * workspace_dev, size_t workspace_bytes, void * stream);
 
+/* The same for 1..3 weights sharing that activation: at decode widths their row tiles form a single GEMV launch
+ * (the reference's fused skinny launch, ggml_cuda_mul_mat_rq_w4a4_fused, patch:2370-2380). */
+int rq_w4a4_mul_mat_quantized_n(const rq_weight_desc * const * w, int n_w, int64_t M, float * const * y_dev,
+                                const int64_t * ldy, int act_group, int path, void * workspace_dev, size_t workspace_bytes,
+                                void * stream);
+
 /* Stage entry points (also used by the parity tests).
  * rq_w4a4_rotate: out[t][:] = x[t][:] * diag(H, H, ...) with H = (H_p kron H_m)/sqrt(n_rot)
  *   (ggml_rq_hadamard per block of n_rot, patch:2450-2485, 2697-2699).

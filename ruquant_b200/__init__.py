@@ -20,7 +20,7 @@ EXPORTS = [
     "rq_w4a4_supported", "rq_hadamard_factor", "rq_w4a4_resolve_clip", "rq_w4a4_act_group", "rq_w4a4_prepack_bytes",
     "rq_w4a4_prepare", "rq_w4a4_workspace_bytes", "rq_w4a4_mul_mat", "rq_w4a4_mul_mat_quantized", "rq_w4a4_rotate",
     "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
-    "rq_w4a4_mul_mat_static",
+    "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n",
 ]
 
 
@@ -67,6 +67,8 @@ def lib():
         L.rq_w4a4_mul_mat.argtypes = [ctypes.POINTER(pd), i32, vp, i64, i64, ctypes.POINTER(vp), ctypes.POINTER(i64), f32, i32,
                                       i32, vp, sz, vp]
         L.rq_w4a4_mul_mat_static.argtypes = [pd, vp, i64, i64, vp, i64, f32, i32, i32, vp]
+        L.rq_w4a4_mul_mat_quantized_n.argtypes = [ctypes.POINTER(pd), i32, i64, ctypes.POINTER(vp), ctypes.POINTER(i64), i32, i32,
+                                                  vp, sz, vp]
         L.rq_w4a4_mul_mat_quantized.argtypes = [pd, i64, vp, i64, i32, i32, vp, sz, vp]
         L.rq_w4a4_rotate.argtypes = [vp, i64, i64, i64, i64, vp, i64, vp]
         L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, vp, sz, vp]
@@ -227,8 +229,22 @@ def quantize(x, n_rot, clip, group=64, workspace=None, stream=None):
 
 
 def mul_mat_quantized(weight, M, workspace, out=None, act_group=64, path=PATH_AUTO, stream=None):
-    """The contraction stage alone, on an activation already quantized into `workspace`."""
+    """The contraction stage alone, on an activation already quantized into `workspace` (a Weight, or a list of up to
+    three sharing that activation, which at decode widths become one launch)."""
     import torch
+    if not isinstance(weight, Weight):
+        ws_list = list(weight)
+        outs = list(out) if out is not None else [torch.empty((M, w.N), dtype=torch.float32, device=workspace.device)
+                                                  for w in ws_list]
+        n_w = len(ws_list)
+        pd = ctypes.POINTER(WeightDesc)
+        descs = (pd * n_w)(*[ctypes.pointer(w.desc) for w in ws_list])
+        ys = (ctypes.c_void_p * n_w)(*[o.data_ptr() for o in outs])
+        ldy = (ctypes.c_int64 * n_w)(*[o.stride(0) for o in outs])
+        with torch.cuda.device(workspace.device):
+            _check(lib().rq_w4a4_mul_mat_quantized_n(descs, n_w, M, ys, ldy, act_group, path, workspace.data_ptr(),
+                                                     workspace.numel(), _stream_ptr(stream)), "rq_w4a4_mul_mat_quantized_n")
+        return outs
     if out is None:
         out = torch.empty((M, weight.N), dtype=torch.float32, device=workspace.device)
     with torch.cuda.device(workspace.device):

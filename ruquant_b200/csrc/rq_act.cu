@@ -515,7 +515,8 @@ cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
         configured[dev] = true;
     }
     const int K = prm.K;
-    if (P > 1 && prm.a8 != nullptr && prm.rot_out == nullptr && prm.G == 64 && prm.m % 64 == 0 && M <= 32) {
+    static const int min_p = getenv("RQ_TUNE_ACT_MINP") ? atoi(getenv("RQ_TUNE_ACT_MINP")) : 0;
+    if (P > 1 && P >= min_p && prm.a8 != nullptr && prm.rot_out == nullptr && prm.G == 64 && prm.m % 64 == 0 && M <= 32) {
         // decode widths: a cluster per token
         const int T = K / (64 * P), NB = P / 4, nchunks = K / prm.m;
         int C = 8;

@@ -257,8 +257,52 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(
     if (tc) {
         RQ_CUDA(rq_launch_gemm_tc(w->tmap_w8, sw, w->wk_mode, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
     } else {
-        const int8_t * wk = w->wk_mode ? reinterpret_cast<const int8_t *>(pp + w->off_wk) : nullptr;
-        RQ_CUDA(rq_launch_gemv(pp + w->off_w4, sw, wk, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
+        rq_gemv_job job;
+        job.w4 = pp + w->off_w4; job.sw = sw; job.N = w->N; job.y = y_dev; job.ldy = ldy;
+        job.wk = w->wk_mode ? reinterpret_cast<const int8_t *>(pp + w->off_wk) : nullptr;
+        RQ_CUDA(rq_launch_gemv(&job, 1, w->K, a8, msh, u, M, act_group, status, stream));
+    }
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized_n(const rq_weight_desc * const * w, int n_w, int64_t M,
+                                           float * const * y_dev, const int64_t * ldy, int act_group, int path,
+                                           void * workspace_dev, size_t workspace_bytes, void * stream) {
+    if (w == nullptr || y_dev == nullptr || ldy == nullptr || n_w < 1 || n_w > RQ_MAX_WEIGHTS) return RQ_ERR_ARG;
+    for (int i = 0; i < n_w; ++i) {
+        if (w[i] == nullptr || y_dev[i] == nullptr) return RQ_ERR_ARG;
+        if (w[i]->K != w[0]->K || w[i]->type != w[0]->type || w[i]->n_rot != w[0]->n_rot) return RQ_ERR_MISMATCH;
+    }
+    if (M < 1) return RQ_ERR_SHAPE;
+    if (act_group != 64 && act_group != 128 && act_group != 256) return RQ_ERR_GROUP;
+    int rc;
+    // decode widths: the weights' row tiles become one GEMV launch when they all have the decode stream and agree on
+    // the weight-multiplier mode (the reference fuses up to three skinny matmuls the same way, patch:308-329)
+    bool one_launch = n_w > 1 && path != RQ_PATH_TC && M <= 16;
+    for (int i = 0; i < n_w && one_launch; ++i) {
+        one_launch = (w[i]->layouts & RQ_PREPACK_DECODE) != 0 && w[i]->wk_mode == w[0]->wk_mode && w[i]->prepack != nullptr &&
+                     ldy[i] >= w[i]->N && !(w[i]->wg64 && act_group != 64);
+    }
+    if (one_launch) {
+        const rq_ws_layout l = rq_ws(w[0]->K, M);
+        if (workspace_dev == nullptr || workspace_bytes < l.bytes) return RQ_ERR_WORKSPACE;
+        uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
+        rq_gemv_job jobs[RQ_MAX_WEIGHTS];
+        for (int i = 0; i < n_w; ++i) {
+            const uint8_t * pp = static_cast<const uint8_t *>(w[i]->prepack);
+            jobs[i].w4 = pp + w[i]->off_w4;
+            jobs[i].sw = reinterpret_cast<const float *>(pp + w[i]->off_sw);
+            jobs[i].wk = w[i]->wk_mode ? reinterpret_cast<const int8_t *>(pp + w[i]->off_wk) : nullptr;
+            jobs[i].N = w[i]->N; jobs[i].y = y_dev[i]; jobs[i].ldy = ldy[i];
+        }
+        RQ_CUDA(rq_launch_gemv(jobs, n_w, w[0]->K, reinterpret_cast<const int8_t *>(ws + l.off_a8),
+                               reinterpret_cast<const int32_t *>(ws + l.off_msh), reinterpret_cast<const float *>(ws + l.off_u), M,
+                               act_group, reinterpret_cast<int32_t *>(ws + l.off_status), (cudaStream_t) stream));
+        return RQ_OK;
+    }
+    for (int i = 0; i < n_w; ++i) {
+        rc = rq_w4a4_mul_mat_quantized(w[i], M, y_dev[i], ldy[i], act_group, path, workspace_dev, workspace_bytes, stream);
+        if (rc != RQ_OK) return rc;
     }
     return RQ_OK;
 }
@@ -275,11 +319,7 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat(const rq_w
     int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group,
                               workspace_dev, workspace_bytes, stream);
     if (rc != RQ_OK) return rc;
-    for (int i = 0; i < n_w; ++i) {
-        rc = rq_w4a4_mul_mat_quantized(w[i], M, y_dev[i], ldy[i], act_group, path, workspace_dev, workspace_bytes, stream);
-        if (rc != RQ_OK) return rc;
-    }
-    return RQ_OK;
+    return rq_w4a4_mul_mat_quantized_n(w, n_w, M, y_dev, ldy, act_group, path, workspace_dev, workspace_bytes, stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream) {

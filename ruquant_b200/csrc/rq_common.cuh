@@ -60,9 +60,17 @@ cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, in
 cudaError_t rq_launch_prepack(const rq_block * blocks, int64_t K, int64_t N, float * sw, uint8_t * w4, int8_t * w8,
                               int8_t * wk, int wk_mode, cudaStream_t stream);
 cudaError_t rq_launch_scan_wk(const rq_block * blocks, int64_t n_blocks, int32_t * flag, cudaStream_t stream);
-cudaError_t rq_launch_gemv(const uint8_t * w4, const float * sw, const int8_t * wk, int64_t K, int64_t N,
-                           const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
-                           float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
+// one weight of a GEMV launch; all jobs of a launch share K, the activation and the weight-multiplier mode
+struct rq_gemv_job {
+    const uint8_t * w4;
+    const float * sw;
+    const int8_t * wk;     // null when every multiplier is 1 (then null for every job of the launch)
+    int64_t N;
+    float * y;
+    int64_t ldy;
+};
+cudaError_t rq_launch_gemv(const rq_gemv_job * jobs, int n_jobs, int64_t K, const int8_t * a8, const int32_t * msh,
+                           const float * u, int64_t M, int G, int32_t * status, cudaStream_t stream);
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mode, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream);

@@ -28,18 +28,34 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], const int (&a)[4], int b0, i
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
-struct GemvParams {
+struct GemvJob {            // one weight of the launch
     const uint4 * w4t;      // [tiles][K/64][32 lanes] x 16 B
     const float * sw;
     const int8_t * wk;      // [N][K/64] or null
+    float * y;
+    int64_t ldy;
+    int N;
+};
+
+// Up to three weights that share the activation (q/k/v, gate/up) are one launch: their row tiles form one list
+// (the reference's multi-weight launch: rq_jobs, ggml/src/ggml-cuda/rq-w4a4-skinny.cuh in patch:1168-1179).
+struct GemvParams {
+    GemvJob job[RQ_MAX_WEIGHTS];
+    int tile_start[RQ_MAX_WEIGHTS + 1];
+    int n_jobs;
     const int8_t * a8;      // [M][K]  8*(q - z)
     const int32_t * msh;    // [M][K/G]  m_g
     const float * u;
-    float * y;
-    int64_t ldy;
     int32_t * status;       // set to 1 when a bounded wait expires
-    int K, N, M, G;
+    int K, M, G;
 };
+
+__device__ __forceinline__ int job_of_tile(const GemvParams & prm, int tile) {
+    int w = 0;
+#pragma unroll
+    for (int i = 1; i < RQ_MAX_WEIGHTS; ++i) if (i < prm.n_jobs && tile >= prm.tile_start[i]) w = i;
+    return w;
+}
 
 constexpr int CH_STEPS = 4;                 // 64-input steps per chunk of the stream
 constexpr int CH_BYTES = CH_STEPS * 512;    // 2 KB: one bulk copy, owned by one consumer warp
@@ -85,7 +101,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
     const int gid = lane >> 2, tig = lane & 3;
     const int K = prm.K, M = prm.M;
     const int ng64 = K >> 6, n_ag = ng64 / GS, nchunks = ng64 / CH_STEPS;
-    const int tiles = (prm.N + 15) / 16;
+    const int tiles = prm.tile_start[prm.n_jobs];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -104,7 +120,8 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
             int issued = 0;       // chunks of this CTA's stream, all tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const uint8_t * src = reinterpret_cast<const uint8_t *>(prm.w4t) + (size_t) tile * ng64 * 512;
+                const int wi = job_of_tile(prm, tile);
+                const uint8_t * src = reinterpret_cast<const uint8_t *>(prm.job[wi].w4t) + (size_t) (tile - prm.tile_start[wi]) * ng64 * 512;
                 for (int c = 0; c < nchunks; ++c) {
                     const int s = issued % STAGES;
                     if (!mbar_wait(smem_u32(&empty[s]), ((issued / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -151,11 +168,13 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 
     int it = 0;                                    // tiles done by this CTA
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-        const int row_lo = tile * 16 + gid, row_hi = row_lo + 8;
+        const int wi = job_of_tile(prm, tile);
+        const GemvJob & jb = prm.job[wi];
+        const int row_lo = (tile - prm.tile_start[wi]) * 16 + gid, row_hi = row_lo + 8;
         const int8_t * kp_lo = nullptr, * kp_hi = nullptr;
         if (HAS_K) {
-            kp_lo = prm.wk + (size_t) (row_lo < prm.N ? row_lo : 0) * ng64;
-            kp_hi = prm.wk + (size_t) (row_hi < prm.N ? row_hi : 0) * ng64;
+            kp_lo = jb.wk + (size_t) (row_lo < jb.N ? row_lo : 0) * ng64;
+            kp_hi = jb.wk + (size_t) (row_hi < jb.N ? row_hi : 0) * ng64;
         }
         int tot[NT][4];
         int acc[NT][4];
@@ -256,8 +275,8 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                 for (int w = 0; w < CONSUMERS; ++w) v += pt[(w * 32 + lane) * 4 * NT + t * 4 + i];
                 tot[t][i] = v;
             }
-        const float s_lo = row_lo < prm.N ? __ldg(prm.sw + row_lo) : 0.0f;
-        const float s_hi = row_hi < prm.N ? __ldg(prm.sw + row_hi) : 0.0f;
+        const float s_lo = row_lo < jb.N ? __ldg(jb.sw + row_lo) : 0.0f;
+        const float s_hi = row_hi < jb.N ? __ldg(jb.sw + row_hi) : 0.0f;
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
 #pragma unroll
@@ -265,8 +284,8 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                 const int tok = 8 * t + 2 * tig + c;
                 if (tok < M) {
                     const float ut = __ldg(prm.u + tok);
-                    if (row_lo < prm.N) prm.y[(size_t) tok * prm.ldy + row_lo] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][c], 16.0f), ut), s_lo);
-                    if (row_hi < prm.N) prm.y[(size_t) tok * prm.ldy + row_hi] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][2 + c], 16.0f), ut), s_hi);
+                    if (row_lo < jb.N) jb.y[(size_t) tok * jb.ldy + row_lo] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][c], 16.0f), ut), s_lo);
+                    if (row_hi < jb.N) jb.y[(size_t) tok * jb.ldy + row_hi] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][2 + c], 16.0f), ut), s_hi);
                 }
             }
         }
@@ -288,7 +307,7 @@ cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int tiles = (prm.N + 15) / 16;
+    const int tiles = prm.tile_start[prm.n_jobs];
     cfg.gridDim = dim3((unsigned) (tiles < 3 * sms ? tiles : 3 * sms));
     cfg.blockDim = dim3((CONSUMERS + 1) * 32);
     cfg.dynamicSmemBytes = smem;
@@ -322,17 +341,27 @@ cudaError_t launch_nt(const GemvParams & prm, bool has_k, cudaStream_t stream) {
 
 }  // namespace
 
-cudaError_t rq_launch_gemv(const uint8_t * w4, const float * sw, const int8_t * wk, int64_t K, int64_t N,
-                           const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
-                           float * y, int64_t ldy, int32_t * status, cudaStream_t stream) {
+cudaError_t rq_launch_gemv(const rq_gemv_job * jobs, int n_jobs, int64_t K, const int8_t * a8, const int32_t * msh,
+                           const float * u, int64_t M, int G, int32_t * status, cudaStream_t stream) {
+    if (n_jobs < 1 || n_jobs > RQ_MAX_WEIGHTS) return cudaErrorInvalidValue;
     // wider inputs go through in passes of 16 tokens, each re-reading the stream
     for (int64_t t0 = 0; t0 < M; t0 += 16) {
         const int mt = (int) (M - t0 < 16 ? M - t0 : 16);
-        GemvParams prm;
-        prm.w4t = reinterpret_cast<const uint4 *>(w4); prm.sw = sw; prm.wk = wk;
-        prm.K = (int) K; prm.N = (int) N; prm.M = mt; prm.G = G;
-        prm.a8 = a8 + t0 * K; prm.msh = msh + t0 * (K / G); prm.u = u + t0; prm.y = y + t0 * ldy; prm.ldy = ldy; prm.status = status;
-        const cudaError_t e = mt <= 8 ? launch_nt<1>(prm, wk != nullptr, stream) : launch_nt<2>(prm, wk != nullptr, stream);
+        GemvParams prm = {};
+        prm.n_jobs = n_jobs;
+        for (int i = 0; i < n_jobs; ++i) {
+            prm.job[i].w4t = reinterpret_cast<const uint4 *>(jobs[i].w4);
+            prm.job[i].sw = jobs[i].sw;
+            prm.job[i].wk = jobs[i].wk;
+            prm.job[i].y = jobs[i].y + t0 * jobs[i].ldy;
+            prm.job[i].ldy = jobs[i].ldy;
+            prm.job[i].N = (int) jobs[i].N;
+            prm.tile_start[i + 1] = prm.tile_start[i] + (int) ((jobs[i].N + 15) / 16);
+        }
+        prm.K = (int) K; prm.M = mt; prm.G = G;
+        prm.a8 = a8 + t0 * K; prm.msh = msh + t0 * (K / G); prm.u = u + t0; prm.status = status;
+        const bool has_k = jobs[0].wk != nullptr;
+        const cudaError_t e = mt <= 8 ? launch_nt<1>(prm, has_k, stream) : launch_nt<2>(prm, has_k, stream);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;

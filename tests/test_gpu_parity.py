@@ -227,6 +227,19 @@ def test_ragged_rows_strides_and_fused_weights(rq, port):
             assert (o[:, w.N:] == -7.0).all(), "wrote past N"
 
 
+@pytest.mark.parametrize("M", [1, 2, 9, 16])
+def test_shared_activation_single_launch(rq, port, M):
+    # q / k / v and gate / up read one activation: one rotate+quantize and one GEMV launch over all their row tiles
+    for K, Ns in [(5120, (6144, 1024, 1024)), (5120, (2176, 2176))]:
+        x = inputs.outlier_activations(M, K, 300 + M)
+        wbs = [port.quantize_weights(inputs.normal_weights(N, K, 310 + i), 45) for i, N in enumerate(Ns)]
+        weights = [rq.Weight(dev(wb).view(-1), 45, K, N=wb.shape[0], layouts=rq.PREPACK_DECODE) for wb in wbs]
+        outs = rq.mul_mat(weights, dev(x))
+        torch.cuda.synchronize()
+        for o, wb in zip(outs, wbs):
+            assert_bits(o.cpu().numpy(), port.mul_mat(wb, 45, K, x), "shared activation M=%d N=%d" % (M, wb.shape[0]))
+
+
 def test_cuda_graph_capture_and_replay(rq, port):
     K, N, M = 5120, 512, 4
     wb = port.quantize_weights(inputs.normal_weights(N, K, 100), 45)
