@@ -58,8 +58,10 @@ __device__ __forceinline__ int job_of_tile(const GemvParams & prm, int tile) {
 }
 
 constexpr int CH_STEPS = 4;                 // 64-input steps per chunk of the stream
-constexpr int CH_BYTES = CH_STEPS * 512;    // 2 KB: one bulk copy, owned by one consumer warp
-constexpr int STAGES = 32;                  // 64 KB ring per CTA
+constexpr int CH_BYTES = CH_STEPS * 512;    // 2 KB: the unit one consumer warp works on
+constexpr int SUBS = 4;                     // chunks per bulk copy
+constexpr int ST_BYTES = SUBS * CH_BYTES;   // 8 KB per bulk copy: few enough copies for a single issuing thread
+constexpr int STAGES = 8;                   // 64 KB ring per CTA
 constexpr int CONSUMERS = 8;                // consumer warps; warp CONSUMERS is the producer
 constexpr long long WAIT_CYCLES = 2000000000ll;
 
@@ -95,18 +97,18 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
     __shared__ uint64_t full[STAGES], empty[STAGES];
     __shared__ int abort_word;
     uint8_t * ring = dyn;
-    int * part = reinterpret_cast<int *>(dyn + STAGES * CH_BYTES);      // [2][CONSUMERS][32][4 * NT]
+    int * part = reinterpret_cast<int *>(dyn + STAGES * ST_BYTES);      // [2][CONSUMERS][32][4 * NT]
     volatile int * abort_flag = &abort_word;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tig = lane & 3;
     const int K = prm.K, M = prm.M;
-    const int ng64 = K >> 6, n_ag = ng64 / GS, nchunks = ng64 / CH_STEPS;
+    const int ng64 = K >> 6, n_ag = ng64 / GS, nchunks = ng64 / CH_STEPS, nst = (nchunks + SUBS - 1) / SUBS;
     const int tiles = prm.tile_start[prm.n_jobs];
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&full[s])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&empty[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(&empty[s])), "r"(SUBS) : "memory");
         }
         abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -115,20 +117,22 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == CONSUMERS) {
-        // ---- producer: bulk copies of 2 KB, gated only by ring space
+        // ---- producer: bulk copies of up to 8 KB, gated only by ring space
         if (lane == 0) {
-            int issued = 0;       // chunks of this CTA's stream, all tiles
+            int issued = 0;       // stages of this CTA's stream, all tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
                 const int wi = job_of_tile(prm, tile);
                 const uint8_t * src = reinterpret_cast<const uint8_t *>(prm.job[wi].w4t) + (size_t) (tile - prm.tile_start[wi]) * ng64 * 512;
-                for (int c = 0; c < nchunks; ++c) {
+                for (int st = 0; st < nst; ++st) {
                     const int s = issued % STAGES;
+                    const int left = nchunks - st * SUBS;
+                    const uint32_t bytes = (uint32_t) (left < SUBS ? left : SUBS) * CH_BYTES;
                     if (!mbar_wait(smem_u32(&empty[s]), ((issued / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full[s]);
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(CH_BYTES) : "memory");
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 :: "r"(smem_u32(ring + (size_t) s * CH_BYTES)), "l"(src + (size_t) c * CH_BYTES), "r"(CH_BYTES), "r"(bar) : "memory");
+                                 :: "r"(smem_u32(ring + (size_t) s * ST_BYTES)), "l"(src + (size_t) st * ST_BYTES), "r"(bytes), "r"(bar) : "memory");
                     ++issued;
                 }
             }
@@ -147,23 +151,19 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // B fragments: token gid (+8 for the second tile); the quantizer stores each run of 64 inputs so that the 16
-    // bytes at offset tig*16 are inputs {0,16,32,48} + tig*4 .. +3: b0, b1 of both MMAs in one 128-bit load
+    // bytes at offset tig*16 are inputs {0,16,32,48} + tig*4 .. +3: b0, b1 of both MMAs in one 128-bit load.
+    // Token slots beyond M read token 0's data: their columns of the product are never stored.
     const uint4 * ap[NT];
-    bool tok_ok[NT];
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-        tok_ok[t] = gid + 8 * t < M;
-        ap[t] = reinterpret_cast<const uint4 *>(prm.a8 + (size_t) (tok_ok[t] ? gid + 8 * t : 0) * K) + tig;
-    }
+    for (int t = 0; t < NT; ++t)
+        ap[t] = reinterpret_cast<const uint4 *>(prm.a8 + (size_t) (gid + 8 * t < M ? gid + 8 * t : 0) * K) + tig;
     const int32_t * mp[NT][2];
-    bool m_ok[NT][2];
 #pragma unroll
     for (int t = 0; t < NT; ++t)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
             const int tok = 8 * t + 2 * tig + c;
-            m_ok[t][c] = tok < M;
-            mp[t][c] = prm.msh + (size_t) (m_ok[t][c] ? tok : 0) * n_ag;
+            mp[t][c] = prm.msh + (size_t) (tok < M ? tok : 0) * n_ag;
         }
 
     int it = 0;                                    // tiles done by this CTA
@@ -183,14 +183,25 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 #pragma unroll
             for (int i = 0; i < 4; ++i) { tot[t][i] = 0; acc[t][i] = 0; }
 
-        // chunk gc of the CTA's stream (all tiles) belongs to consumer warp gc % CONSUMERS
-        const int gc0 = it * nchunks;
+        // stage gs of the CTA's stream (all tiles) is shared by four consumer warps, one chunk each: warps 0-3 take
+        // the even stages, warps 4-7 the odd ones
+        const int gs0 = it * nst, sc = warp & 3;
         bool ok = true;
-        for (int c = ((warp - gc0) % CONSUMERS + CONSUMERS) % CONSUMERS; c < nchunks; c += CONSUMERS) {
-            const int gc = gc0 + c, s = gc % STAGES;
+        for (int st = ((warp >> 2) - gs0) & 1; st < nst; st += 2) {
+            const int gs = gs0 + st, s = gs % STAGES;
+            const int c = st * SUBS + sc;                 // this warp's chunk of the tile (may lie beyond its end)
+            // the activations do not depend on the weights: fetch them while the stage is still in flight
+            uint4 bq[CH_STEPS][NT];
+            if (c < nchunks) {
+#pragma unroll
+                for (int q = 0; q < CH_STEPS; ++q)
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) bq[q][t] = __ldg(ap[t] + (c * CH_STEPS + q) * 4);
+            }
             // the MMAs below are warp-collective: leave the loop together or not at all
-            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full[s]), (gc / STAGES) & 1, abort_flag))) { ok = false; break; }
-            const uint4 * sp_ = reinterpret_cast<const uint4 *>(ring + (size_t) s * CH_BYTES) + lane;
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full[s]), (gs / STAGES) & 1, abort_flag))) { ok = false; break; }
+            if (c < nchunks) {
+            const uint4 * sp_ = reinterpret_cast<const uint4 *>(ring + (size_t) s * ST_BYTES + (size_t) sc * CH_BYTES) + lane;
             // The integer MMA of this part has a long latency: issue the MMAs of SP steps (two per step, on
             // independent zero-initialised accumulators) before touching any result.
             constexpr int SP = NT == 1 ? 4 : 2;
@@ -203,7 +214,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                     const uint4 wv = sp_[(h + sp) * 32];
                     uint4 b[NT];
 #pragma unroll
-                    for (int t = 0; t < NT; ++t) b[t] = tok_ok[t] ? __ldg(ap[t] + j * 4) : make_uint4(0u, 0u, 0u, 0u);
+                    for (int t = 0; t < NT; ++t) b[t] = bq[h + sp][t];
                     // words 0,1 -> first 32 inputs (a0..a3), words 2,3 -> second 32 inputs
                     int a0[4], a1[4];
                     a0[0] = (int) ((wv.x << 4) & 0xF0F0F0F0u); a0[1] = (int) (wv.x & 0xF0F0F0F0u);
@@ -223,15 +234,19 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 #pragma unroll
                     for (int t = 0; t < NT; ++t)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) acc[t][i] += pa[sp][0][t][i] + pa[sp][1][t][i];
+                        for (int i = 0; i < 4; ++i) {
+                            if (ONE && (i & 1)) continue;                 // token 1 of the pair does not exist
+                            if (GS == 1) acc[t][i] = pa[sp][0][t][i] + pa[sp][1][t][i];
+                            else         acc[t][i] += pa[sp][0][t][i] + pa[sp][1][t][i];
+                        }
                     if ((st % GS) == GS - 1) {
                         const int ag = j / GS;
                         int klo = 1, khi = 1;
                         if (HAS_K) { klo = kp_lo[j]; khi = kp_hi[j]; }
 #pragma unroll
                         for (int t = 0; t < NT; ++t) {
-                            const int m0 = m_ok[t][0] ? __ldg(mp[t][0] + ag) : 0;
-                            const int m1 = (!ONE && m_ok[t][1]) ? __ldg(mp[t][1] + ag) : 0;
+                            const int m0 = __ldg(mp[t][0] + ag);
+                            const int m1 = ONE ? 0 : __ldg(mp[t][1] + ag);
                             if (HAS_K) {
                                 tot[t][0] += (klo * m0 * (acc[t][0] >> 7)) >> 4;
                                 tot[t][2] += (khi * m0 * (acc[t][2] >> 7)) >> 4;
@@ -247,11 +262,14 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                                     tot[t][3] += (m1 * acc[t][3]) >> RQ_FOLD_SHIFT;
                                 }
                             }
+                            if (GS > 1) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+                                for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+                            }
                         }
                     }
                 }
+            }
             }
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&empty[s])) : "memory");
@@ -295,20 +313,26 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 template <int NT, int GS, bool HAS_K, bool ONE>
 cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
     static bool configured[64] = {};
-    const size_t smem = (size_t) STAGES * CH_BYTES + 2 * (size_t) CONSUMERS * 32 * 4 * NT * sizeof(int);
+    static int per_sm[64] = {};
+    const size_t smem = (size_t) STAGES * ST_BYTES + 2 * (size_t) CONSUMERS * 32 * 4 * NT * sizeof(int);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
         e = cudaFuncSetAttribute(rq_gemv_mma_kernel<NT, GS, HAS_K, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return e;
+        // persistent grid: as many CTAs as are resident at once
+        int nb = 0, sms = 148;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE>, (CONSUMERS + 1) * 32, smem);
+        if (e != cudaSuccess) return e;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        per_sm[dev] = (nb > 0 ? nb : 1) * sms;
         configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = prm.tile_start[prm.n_jobs];
-    cfg.gridDim = dim3((unsigned) (tiles < 3 * sms ? tiles : 3 * sms));
+    const int resident = dev < 64 ? per_sm[dev] : 148;
+    cfg.gridDim = dim3((unsigned) (tiles < resident ? tiles : resident));
     cfg.blockDim = dim3((CONSUMERS + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
