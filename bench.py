@@ -12,8 +12,8 @@ through the C ABI with host buffers: pinned-host -> device copies of the step's 
 copies of its outputs inside the timed region.  `prefill` reports the M = 4096 gate/up-shaped GEMM
 (K=5120, N=17408) in TOPS, whole node (rotate + quantize + tcgen05 GEMM + fold + epilogue).
 
-With N GPUs the weight rows are sharded along N, the activation is replicated and each matmul's output is
-assembled with an NCCL all-gather (total work fixed: "strong" scaling).
+With N GPUs the weight rows are sharded along N, the activations are replicated and each layer's output (its seven
+matmul outputs side by side) is assembled with one NCCL all-gather (total work fixed: "strong" scaling).
 """
 import argparse
 import json
@@ -166,9 +166,16 @@ def run_ours(args):
     # decoder: attention input -> q, k, v; attention output -> o; MLP input -> gate, up; MLP hidden -> down.  Weights
     # that share an activation go through one call (one rotate+quantize, one GEMV launch over all their row tiles),
     # the reference's fused launch for such matmuls (ggml_cuda_try_fuse).
-    groups = []        # (K, x_dev, workspace, [(N_total, N_local, Weight, y_local, y_full)])
+    groups = []        # (K, x_dev, workspace, [(N_total, N_local, Weight, y_local, y_full)], gather or None)
     mats = []          # flat list of (K, N_total) for the byte count
+    n_layer_local = sum(N // world for _n, _k, N in LAYER)
+    layer_bufs = []
     for layer in range(L):
+        # the layer's seven local outputs sit side by side, so that one all-gather assembles the layer's output
+        y_layer_loc = torch.empty((n_layer_local,), device=dev, dtype=torch.float32)
+        layer_bufs.append(y_layer_loc)
+        y_layer_all = torch.empty((world * n_layer_local,), device=dev, dtype=torch.float32) if world > 1 else None
+        col = 0
         for gi, names in enumerate(GROUPS):
             K = LAYER_DIMS[names[0]][0]
             g = torch.Generator(device=dev)
@@ -183,27 +190,27 @@ def run_ours(args):
                 w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_DECODE)
                 w.blocks = None      # the kernels read only the prepacked stream
                 del blocks
-                y_full = torch.empty((1, N), device=dev, dtype=torch.float32)
-                y_loc = y_full if world == 1 else torch.empty((1, nl), device=dev, dtype=torch.float32)
-                members.append((N, nl, w, y_loc, y_full))
+                y_loc = y_layer_loc[col:col + nl].view(1, nl)
+                col += nl
+                members.append((N, nl, w, y_loc, y_loc))
                 mats.append((K, N))
-            groups.append((K, x, rq.new_workspace(K, 1, dev), members))
+            last = gi == len(GROUPS) - 1
+            groups.append((K, x, rq.new_workspace(K, 1, dev), members, (y_layer_all, y_layer_loc) if (world > 1 and last) else None))
     torch.cuda.synchronize()
     # algorithmic bytes: every weight block and every output once, every activation once per group that shares it
     total_bytes = sum(N * (K // 256) * 144 + 4 * N for (K, N) in mats) + sum(4 * K for (K, *_r) in groups)
     stream = torch.cuda.Stream(device=dev)
 
     def enqueue_pass(quantize=True):
-        for K, x, ws, members in groups:
+        for K, x, ws, members, gather in groups:
             weights = [m[2] for m in members]
             outs = [m[3] for m in members]
             if quantize:
                 rq.mul_mat(weights, x, out=outs, clip=1.0, act_group=64, workspace=ws, stream=stream)
             else:
                 rq.mul_mat_quantized(weights, 1, ws, out=outs, act_group=64, stream=stream)
-            if world > 1:
-                for N, nl, w, y_loc, y_full in members:
-                    dist.all_gather_into_tensor(y_full.view(-1), y_loc.view(-1))
+            if gather is not None:       # end of a layer: every rank gets every rank's slice of the layer's output
+                dist.all_gather_into_tensor(gather[0], gather[1])
 
     def capture(fn):
         g = torch.cuda.CUDAGraph()
@@ -257,17 +264,19 @@ def run_ours(args):
 
     # ---- end to end through the C ABI with host buffers
     x_host = [torch.randn((1, K), dtype=torch.float32).pin_memory() for (K, *_r) in groups]
-    y_host = [[torch.empty((1, m[0]), dtype=torch.float32).pin_memory() for m in members] for (_K, _x, _ws, members) in groups]
+    # the step's result on the host: per layer the assembled output of all ranks (shard-major when N > 1)
+    layer_out = [g[4][0] if g[4] is not None else None for g in groups]
+    y_host = [torch.empty((world * n_layer_local,), dtype=torch.float32).pin_memory() for _ in range(L)]
     h2d = sum(x.numel() * 4 for x in x_host)
-    d2h = sum(y.numel() * 4 for ys in y_host for y in ys)
+    d2h = sum(y.numel() * 4 for y in y_host)
 
     def e2e_step():
-        for (K, x, ws, members), xh in zip(groups, x_host):
+        for (K, x, ws, members, gather), xh in zip(groups, x_host):
             x.copy_(xh, non_blocking=True)
         g_pass.replay()
-        for (K, x, ws, members), yhs in zip(groups, y_host):
-            for m, yh in zip(members, yhs):
-                yh.copy_(m[4], non_blocking=True)
+        for li in range(L):
+            src = layer_out[4 * li + 3] if world > 1 else layer_bufs[li]
+            y_host[li].copy_(src, non_blocking=True)
 
     ms_e2e = timed(e2e_step, args.steps, args.warmup)
     e2e = {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -322,14 +331,20 @@ def run_ours(args):
                            "weights_gb": sum(N * (K // 256) * 144 for (K, N) in mats) / 1e9,
                            "activation_sharing": "q,k,v | o | gate,up | down: one rotate+quantize and one GEMV launch per group",
                            "l2": "inputs larger than L2 (weights streamed once per step)",
-                           "parallelism": "N-sharded x%d, NCCL all-gather per matmul" % world if world > 1 else "single GPU",
+                           "parallelism": "N-sharded x%d, one NCCL all-gather per layer output" % world if world > 1 else "single GPU",
                            "cuda_graph": True},
                 "frac_of_hbm_peak": value / (hbm_peak * world), "peak_kind": "of " + peak_kind,
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "prefill": prefill, "clocks": clocks,
                 "gpu_launches": 2 * len(groups) * args.steps}
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # every rank is past its last collective: leave without tearing NCCL down under the captured graphs
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_single(args):

@@ -253,11 +253,11 @@ struct ActParams {
 // =====================================================================================  one CTA per token
 // P > 1: Paley order (compile time); P == 1: no Paley stage (plain W4A4, or a power-of-two rotation).
 // shared memory: [K floats row][P*P floats sign table]
-template <int P>
-__global__ void __launch_bounds__(ACT_THREADS) rq_act_kernel(const ActParams prm) {
+template <int P, int THREADS>
+__global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
     extern __shared__ __align__(16) float buf[];
     __shared__ float g_lo[512], g_hi[512];
-    __shared__ float red[ACT_THREADS / 32];
+    __shared__ float red[THREADS / 32];
     __shared__ signed char chi[128];
     const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int K = prm.K;
@@ -498,8 +498,13 @@ constexpr size_t SMEM_LIMIT = 220 * 1024;
 
 template <int P>
 cudaError_t configure() {
-    cudaError_t e = cudaFuncSetAttribute(rq_act_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
-    if (e != cudaSuccess || P == 1) return e;
+    cudaError_t e = cudaFuncSetAttribute(rq_act_kernel<P, ACT_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
+    if (e != cudaSuccess) return e;
+    if (P <= 20) {
+        e = cudaFuncSetAttribute(rq_act_kernel<(P <= 20 ? P : 1), 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+    }
+    if (P == 1) return e;
     return cudaFuncSetAttribute(rq_act_cluster_kernel<(P > 1 ? P : 12)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
 }
 
@@ -531,7 +536,10 @@ cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
     }
     const size_t smem = ((size_t) K + (P > 1 ? (size_t) P * P : 0)) * sizeof(float);
     if (smem > SMEM_LIMIT) return cudaErrorInvalidValue;
-    return launch_ex(rq_act_kernel<P>, dim3((unsigned) M), dim3(ACT_THREADS), smem, 1, stream, prm);
+    // few tokens and a cheap Paley stage: one big CTA per token keeps every phase short
+    static const int wide = getenv("RQ_TUNE_ACT_WIDE") ? atoi(getenv("RQ_TUNE_ACT_WIDE")) : 1;
+    if (P <= 20 && M <= 64 && wide) return launch_ex(rq_act_kernel<(P <= 20 ? P : 1), 1024>, dim3((unsigned) M), dim3(1024), smem, 1, stream, prm);
+    return launch_ex(rq_act_kernel<P, ACT_THREADS>, dim3((unsigned) M), dim3(ACT_THREADS), smem, 1, stream, prm);
 }
 
 }  // namespace
