@@ -54,7 +54,7 @@ typedef enum rq_status {
 #define RQ_PREPACK_ALL     3
 
 /* kernel selection of rq_w4a4_mul_mat */
-#define RQ_PATH_AUTO  0        /* M <= 16: GEMV; else tcgen05 GEMM if prepacked for it, else chunked GEMV */
+#define RQ_PATH_AUTO  0        /* M <= 64: GEMV in passes of 16 tokens; else tcgen05 GEMM if prepacked for it */
 #define RQ_PATH_GEMV  1
 #define RQ_PATH_TC    2
 

@@ -22,6 +22,7 @@
 #include <stdlib.h>
 
 #include "rq_common.cuh"
+#include "rq_act_dev.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -29,213 +30,8 @@ namespace {
 
 constexpr int ACT_THREADS = 256;
 
-// ---- Paley-I signs: A = I + S, S[0][a>0] = +1, S[i>0][0] = -1, S[i][a] = chi((a - i) mod q)   (rq_paley, patch:2432-2448)
-// table[i * p + a] = +1.0f / -1.0f for "add" / "subtract" of input chunk i into output chunk a
-__device__ void build_sign_table(float * table, signed char * chi, int p, int tid, int nt) {
-    const int q = p - 1;
-    for (int r = tid; r < q; r += nt) chi[r] = r == 0 ? 0 : -1;
-    __syncthreads();
-    for (int r = tid + 1; r < q; r += nt) chi[(r * r) % q] = 1;
-    __syncthreads();
-    for (int e = tid; e < p * p; e += nt) {
-        const int i = e / p, a = e - i * p;
-        bool plus;
-        if (i == a || i == 0) plus = true;
-        else if (a == 0) plus = false;
-        else plus = chi[(((a - i) % q) + q) % q] > 0;
-        table[e] = plus ? 1.0f : -1.0f;
-    }
-}
+using namespace rq_act_dev;
 
-// outputs a0 .. a0+3 of one column held in registers: four independent chains, terms in ascending i
-template <int P>
-__device__ __forceinline__ void paley_block4(const float (&col)[P], const float * __restrict__ table, int a0, float scale,
-                                             float (&out)[4]) {
-    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
-#pragma unroll
-    for (int i = 0; i < P; ++i) {
-        const float4 s = *reinterpret_cast<const float4 *>(table + i * P + a0);
-        acc0 = __fmaf_rn(col[i], s.x, acc0);
-        acc1 = __fmaf_rn(col[i], s.y, acc1);
-        acc2 = __fmaf_rn(col[i], s.z, acc2);
-        acc3 = __fmaf_rn(col[i], s.w, acc3);
-    }
-    out[0] = __fmul_rn(acc0, scale);
-    out[1] = __fmul_rn(acc1, scale);
-    out[2] = __fmul_rn(acc2, scale);
-    out[3] = __fmul_rn(acc3, scale);
-}
-
-// One radix-R pass of the Sylvester transform over a buffer of whole chunks: elements base + j*s, j < R, go through
-// log2(R) butterfly stages of strides s, 2s, 4s (the reference's order, h ascending; each stage is c[k] = a + b,
-// c[k+h] = a - b with k the lower index, patch:2456-2463).
-template <int R>
-__device__ __forceinline__ void fwht_pass(float * buf, int len, int ls, int tid, int nt) {
-    const int s = 1 << ls;
-    for (int q = tid; q < len / R; q += nt) {
-        const int hi = q >> ls, lo = q & (s - 1);
-        float * b = buf + (size_t) hi * s * R + lo;
-        float v[R];
-#pragma unroll
-        for (int j = 0; j < R; ++j) v[j] = b[j * s];
-#pragma unroll
-        for (int d = 1; d < R; d <<= 1) {
-#pragma unroll
-            for (int j = 0; j < R; ++j) {
-                if ((j & d) == 0) {
-                    const float a = v[j], c = v[j + d];
-                    v[j] = __fadd_rn(a, c);
-                    v[j + d] = __fsub_rn(a, c);
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < R; ++j) b[j * s] = v[j];
-    }
-}
-
-__device__ __forceinline__ void fwht_chunks(float * buf, int len, int m, int tid, int nt) {
-    for (int ls = 0; (1 << ls) < m; ls += 3) {
-        const int rem = m >> ls;
-        if (rem >= 8) fwht_pass<8>(buf, len, ls, tid, nt);
-        else if (rem == 4) fwht_pass<4>(buf, len, ls, tid, nt);
-        else fwht_pass<2>(buf, len, ls, tid, nt);
-        __syncthreads();
-    }
-}
-
-// Sylvester transform of 32*EPT consecutive values held by one warp, lane l owning values [l*EPT, (l+1)*EPT): the
-// strides below EPT are butterflies between a lane's own registers, the strides EPT .. 16*EPT are exchanges with lane
-// l ^ d (the lower lane forms a + b, the upper lane a - b with a the lower lane's value) -- the same operations in the
-// same order as the reference's loop, without touching shared memory.
-template <int EPT>
-__device__ __forceinline__ void fwht_warp(float (&v)[EPT], int lane) {
-#pragma unroll
-    for (int d = 1; d < EPT; d <<= 1) {
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            if ((j & d) == 0) {
-                const float a = v[j], c = v[j + d];
-                v[j] = __fadd_rn(a, c);
-                v[j + d] = __fsub_rn(a, c);
-            }
-        }
-    }
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const bool upper = (lane & d) != 0;
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j], d);
-            v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
-        }
-    }
-}
-
-// global -> (transform) -> shared for `count` runs of 32*EPT floats, one warp per run
-template <int EPT>
-__device__ __forceinline__ void load_transform_runs(const float * __restrict__ src, float * dst, int count, bool transform,
-                                                    int warp, int nwarps, int lane) {
-    for (int r = warp; r < count; r += nwarps) {
-        const float * s = src + (size_t) r * 32 * EPT + lane * EPT;
-        float * d = dst + (size_t) r * 32 * EPT + lane * EPT;
-        float v[EPT];
-        if constexpr (EPT >= 4) {
-#pragma unroll
-            for (int j = 0; j < EPT; j += 4) {
-                const float4 q = __ldg(reinterpret_cast<const float4 *>(s + j));
-                v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < EPT; ++j) v[j] = __ldg(s + j);
-        }
-        if (transform) fwht_warp<EPT>(v, lane);
-        if constexpr (EPT >= 4) {
-#pragma unroll
-            for (int j = 0; j < EPT; j += 4) *reinterpret_cast<float4 *>(d + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < EPT; ++j) d[j] = v[j];
-        }
-    }
-}
-
-// A buffer of `len` floats made of whole chunks of m: loaded from global memory and Sylvester-transformed chunk by
-// chunk.  Chunks up to 1024 wide are done entirely in registers and shuffles; wider chunks finish their upper
-// strides (1024 and above, conflict-free) in shared memory.  Ends with a CTA barrier.
-__device__ __forceinline__ void load_fwht(const float * __restrict__ src, float * dst, int len, int m, int tid, int nt) {
-    const int warp = tid >> 5, nwarps = nt >> 5, lane = tid & 31;
-    const int run = m < 1024 ? m : 1024;
-    switch (run) {
-        case 32:   load_transform_runs<1>(src, dst, len / 32, m > 1, warp, nwarps, lane); break;
-        case 64:   load_transform_runs<2>(src, dst, len / 64, true, warp, nwarps, lane); break;
-        case 128:  load_transform_runs<4>(src, dst, len / 128, true, warp, nwarps, lane); break;
-        case 256:  load_transform_runs<8>(src, dst, len / 256, true, warp, nwarps, lane); break;
-        case 512:  load_transform_runs<16>(src, dst, len / 512, true, warp, nwarps, lane); break;
-        case 1024: load_transform_runs<32>(src, dst, len / 1024, true, warp, nwarps, lane); break;
-        default: {   // m < 32 (1 .. 16): plain copy, then the generic passes
-            for (int i = tid; i < len; i += nt) dst[i] = __ldg(src + i);
-            __syncthreads();
-            fwht_chunks(dst, len, m, tid, nt);
-            return;
-        }
-    }
-    __syncthreads();
-    for (int ls = 10; (1 << ls) < m; ls += 3) {
-        const int rem = m >> ls;
-        if (rem >= 8) fwht_pass<8>(dst, len, ls, tid, nt);
-        else if (rem == 4) fwht_pass<4>(dst, len, ls, tid, nt);
-        else fwht_pass<2>(dst, len, ls, tid, nt);
-        __syncthreads();
-    }
-}
-
-// the chunks a cluster CTA owns (global chunk rank + s*C -> local slot s), one warp per run of 32*EPT values
-template <int EPT>
-__device__ __forceinline__ void cluster_chunks(const float * __restrict__ xrow, float * chunks, int rank, int C, int nloc, int m,
-                                               int tid, int nt) {
-    const int warp = tid >> 5, nwarps = nt >> 5, lane = tid & 31;
-    const int rpc = m / (32 * EPT);                          // runs per chunk (1 up to m = 1024)
-    for (int r = warp; r < nloc * rpc; r += nwarps) {
-        const int s = r / rpc, sr = r - s * rpc;
-        load_transform_runs<EPT>(xrow + (size_t) (rank + s * C) * m + (size_t) sr * 32 * EPT,
-                                 chunks + (size_t) s * m + (size_t) sr * 32 * EPT, 1, true, 0, 1, lane);
-    }
-}
-
-// ---- quantizer pieces shared by both kernels
-
-// range of a word of 8 values reduced over the lpg lanes that share its group
-__device__ __forceinline__ void group_range(const float4 a, const float4 b, int lpg, float clip, float & lo, float & hi) {
-    float mn = fminf(fminf(fminf(a.x, a.y), fminf(a.z, a.w)), fminf(fminf(b.x, b.y), fminf(b.z, b.w)));
-    float mx = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
-    mn = fminf(mn, 0.0f);
-    mx = fmaxf(mx, 0.0f);
-    for (int o = 1; o < lpg; o <<= 1) {
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    }
-    lo = __fmul_rn(mn, clip);
-    hi = __fmul_rn(mx, clip);
-}
-
-// the 8 codes of a word as int8 8*(q - z) and the group's multiplier
-__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, int & mi) {
-    const float mf = fminf(fmaxf(ceilf(__fdiv_rn(__fmul_rn(__fsub_rn(hi, lo), 255.0f), R)), 1.0f), 255.0f);
-    mi = (int) mf;
-    const float inv = __fdiv_rn(1.0f, __fmul_rn((float) mi, unit));
-    const float zf = fminf(fmaxf(rintf(__fmul_rn(-lo, inv)), 0.0f), 15.0f);
-    const float v[8] = { a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w };
-    uint32_t pk[2] = { 0u, 0u };
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float qf = fminf(fmaxf(__fadd_rn(rintf(__fmul_rn(v[j], inv)), zf), 0.0f), 15.0f);
-        const int d = RQ_ACT_SCALE * ((int) qf - (int) zf);   // 8*(q - z) in [-120, 120]
-        pk[j >> 2] |= (uint32_t) (d & 0xFF) << (8 * (j & 3));
-    }
-    return make_uint2(pk[0], pk[1]);
-}
 
 struct ActParams {
     const float * x;

@@ -251,7 +251,8 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(
     bool tc;
     if (path == RQ_PATH_GEMV) { if (!has_dec) return RQ_ERR_ARG; tc = false; }
     else if (path == RQ_PATH_TC) { if (!has_pre) return RQ_ERR_ARG; tc = true; }
-    else if (path == RQ_PATH_AUTO) tc = has_pre && (M > 16 || !has_dec);
+    // up to 64 tokens the GEMV in passes of 16 (the later passes read the stream from L2) beats a 128-token MMA tile
+    else if (path == RQ_PATH_AUTO) tc = has_pre && (M > 64 || !has_dec);
     else return RQ_ERR_ARG;
     int32_t * status = reinterpret_cast<int32_t *>(const_cast<uint8_t *>(ws) + l.off_status);
     if (tc) {
@@ -278,7 +279,7 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized_
     int rc;
     // decode widths: the weights' row tiles become one GEMV launch when they all have the decode stream and agree on
     // the weight-multiplier mode (the reference fuses up to three skinny matmuls the same way, patch:308-329)
-    bool one_launch = n_w > 1 && path != RQ_PATH_TC && M <= 16;
+    bool one_launch = n_w > 1 && path != RQ_PATH_TC && M <= 64;
     for (int i = 0; i < n_w && one_launch; ++i) {
         one_launch = (w[i]->layouts & RQ_PREPACK_DECODE) != 0 && w[i]->wk_mode == w[0]->wk_mode && w[i]->prepack != nullptr &&
                      ldy[i] >= w[i]->N && !(w[i]->wg64 && act_group != 64);
