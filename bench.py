@@ -396,7 +396,7 @@ def run_single(args):
 
     def quant_only():
         for w in weights:
-            rq.quantize(x, w.n_rot, 1.0, G, workspace=ws, stream=stream)
+            rq.quantize(x, w.n_rot, 1.0, G, workspace=ws, stream=stream, fmt=rq.act_format(w, M, args.path))
 
     def timed(fn):
         g = torch.cuda.CUDAGraph()

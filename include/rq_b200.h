@@ -53,6 +53,11 @@ typedef enum rq_status {
 #define RQ_PREPACK_PREFILL 2   /* int8 operand for the tcgen05 GEMM           (K*N bytes)   */
 #define RQ_PREPACK_ALL     3
 
+/* how rq_w4a4_quantize stores the activation: int8 8*(q - z) for the GEMV and the integer tensor-core kernel,
+ * or e4m3 (q - z) for the fp8 tensor-core kernel (weights without multipliers, the usual case) */
+#define RQ_FMT_I8   0
+#define RQ_FMT_E4M3 1
+
 /* kernel selection of rq_w4a4_mul_mat */
 #define RQ_PATH_AUTO  0        /* M <= 64: GEMV in passes of 16 tokens; else tcgen05 GEMM if prepacked for it */
 #define RQ_PATH_GEMV  1
@@ -131,13 +136,19 @@ int rq_w4a4_mul_mat_quantized_n(const rq_weight_desc * const * w, int n_w, int64
  * rq_w4a4_rotate: out[t][:] = x[t][:] * diag(H, H, ...) with H = (H_p kron H_m)/sqrt(n_rot)
  *   (ggml_rq_hadamard per block of n_rot, patch:2450-2485, 2697-2699).
  * rq_w4a4_quantize: rotate (n_rot > 0) and quantize M tokens into the workspace
- *   (quantize_row_a4_clip / quantize_row_a4h_clip_n, patch:2639-2679, 2720-2736). */
+ *   (quantize_row_a4_clip / quantize_row_a4h_clip_n, patch:2639-2679, 2720-2736); act_format as returned by
+ *   rq_w4a4_act_format.  The contraction kernels check the recorded format and refuse a mismatch (status). */
 int rq_w4a4_rotate(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float * out_dev, int64_t ldo,
                    void * stream);
 int rq_w4a4_quantize(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float clip, int act_group,
-                     void * workspace_dev, size_t workspace_bytes, void * stream);
+                     int act_format, void * workspace_dev, size_t workspace_bytes, void * stream);
 
-/* Where the quantized activation sits in the workspace: a8 = int8 [M][K] holding 8*(q - z_g),
+/* The activation format (RQ_FMT_*) the contraction of these weights at M tokens wants -- what rq_w4a4_mul_mat passes
+ * to the quantizer itself; for callers that run rq_w4a4_quantize and rq_w4a4_mul_mat_quantized separately.
+ * Negative rq_status on a request that cannot be served (missing layout, weights that need different formats). */
+int rq_w4a4_act_format(const rq_weight_desc * const * w, int n_w, int64_t M, int path);
+
+/* Where the quantized activation sits in the workspace (RQ_FMT_I8): a8 = int8 [M][K] holding 8*(q - z_g),
  * permuted inside each run of 64 inputs (piece 16*i + 4*t .. +3 at byte 16*t + 4*i); msh = int32
  * [M][K/act_group] holding m_g; u = f32 [M] token units. */
 int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off_a8, uint64_t * off_msh, uint64_t * off_u,

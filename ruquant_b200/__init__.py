@@ -15,12 +15,13 @@ TYPE_W4A4, TYPE_W4A4H = 44, 45
 BLOCK_CODES, BLOCK_BYTES = 256, 144
 PREPACK_DECODE, PREPACK_PREFILL, PREPACK_ALL = 1, 2, 3
 PATH_AUTO, PATH_GEMV, PATH_TC = 0, 1, 2
+FMT_I8, FMT_E4M3 = 0, 1
 
 EXPORTS = [
     "rq_w4a4_supported", "rq_hadamard_factor", "rq_w4a4_resolve_clip", "rq_w4a4_act_group", "rq_w4a4_prepack_bytes",
     "rq_w4a4_prepare", "rq_w4a4_workspace_bytes", "rq_w4a4_mul_mat", "rq_w4a4_mul_mat_quantized", "rq_w4a4_rotate",
     "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
-    "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n",
+    "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n", "rq_w4a4_act_format",
 ]
 
 
@@ -71,7 +72,8 @@ def lib():
                                                   vp, sz, vp]
         L.rq_w4a4_mul_mat_quantized.argtypes = [pd, i64, vp, i64, i32, i32, vp, sz, vp]
         L.rq_w4a4_rotate.argtypes = [vp, i64, i64, i64, i64, vp, i64, vp]
-        L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, vp, sz, vp]
+        L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, i32, vp, sz, vp]
+        L.rq_w4a4_act_format.argtypes = [ctypes.POINTER(pd), i32, i64, i32]
         u64p = ctypes.POINTER(ctypes.c_uint64)
         L.rq_w4a4_workspace_layout.argtypes = [i64, i64, i32, u64p, u64p, u64p, u64p]
         L.rq_w4a4_device_status.argtypes = [vp, i64, i64, vp]
@@ -216,14 +218,24 @@ def rotate(x, n_rot, stream=None):
     return out
 
 
-def quantize(x, n_rot, clip, group=64, workspace=None, stream=None):
-    """Rotate (n_rot > 0) and quantize; returns (workspace, a8, msh, u)."""
+def act_format(weights, M, path=PATH_AUTO):
+    """The activation format (FMT_*) the contraction of these weights at M tokens consumes."""
+    ws_list = [weights] if isinstance(weights, Weight) else list(weights)
+    pd = ctypes.POINTER(WeightDesc)
+    descs = (pd * len(ws_list))(*[ctypes.pointer(w.desc) for w in ws_list])
+    fmt = lib().rq_w4a4_act_format(descs, len(ws_list), M, path)
+    _check(min(fmt, 0), "rq_w4a4_act_format")
+    return fmt
+
+
+def quantize(x, n_rot, clip, group=64, workspace=None, stream=None, fmt=FMT_I8):
+    """Rotate (n_rot > 0) and quantize; returns (workspace, a8, msh, u) (the views decode the FMT_I8 layout)."""
     M, K = x.shape
     if workspace is None:
         workspace = new_workspace(K, M, x.device)
     import torch
     with torch.cuda.device(x.device):
-        _check(lib().rq_w4a4_quantize(x.data_ptr(), x.stride(0), M, K, n_rot, clip, group, workspace.data_ptr(),
+        _check(lib().rq_w4a4_quantize(x.data_ptr(), x.stride(0), M, K, n_rot, clip, group, fmt, workspace.data_ptr(),
                                       workspace.numel(), _stream_ptr(stream)), "rq_w4a4_quantize")
     return (workspace,) + workspace_views(workspace, K, M, group)
 

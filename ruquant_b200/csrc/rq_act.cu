@@ -8,7 +8,8 @@
 //              acc + x / acc - x, and the sign becomes data (a table in shared memory) instead of code.
 //   quantizer  rq_quantize_row_a, patch:2639-2679.
 // Output layout (what the contraction kernels consume): int8 8*(q - z_g) [M][K] (permuted inside each run of 64
-// inputs, see rq_perm64), int32 m_g [M][K/G], f32 u [M].
+// inputs, see rq_perm64), int32 m_g [M][K/G], f32 u [M]; for the fp8 tensor-core path instead the e4m3 byte of
+// (q - z_g) and the f32 bits of m_g / 16.
 //
 // Two kernels:
 //   rq_act_kernel<P>          one CTA per token, the token's row resident in shared memory (prefill widths, any G).
@@ -36,7 +37,7 @@ using namespace rq_act_dev;
 struct ActParams {
     const float * x;
     int64_t ldx;
-    int K, n_rot, p, m, G;
+    int K, n_rot, p, m, G, fmt;
     float rot_scale, clip;
     int8_t * a8;
     int32_t * msh;
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if constexpr (P > 1) build_sign_table(table, chi, P, tid, nt);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (t == 0 && tid == 0 && prm.status != nullptr) *prm.status = 0;
+    if (t == 0 && tid == 0 && prm.status != nullptr) { prm.status[0] = 0; prm.status[1] = prm.fmt; }
 
     const float * xrow = prm.x + (int64_t) t * prm.ldx;
     if (prm.n_rot > 0) {
@@ -127,11 +128,11 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
         const int g = w / lpg;
         int mi;
         const uint2 pk = encode_word(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1],
-                                     g_lo[g], g_hi[g], R, unit, mi);
+                                     g_lo[g], g_hi[g], R, unit, prm.fmt, mi);
         const int kw = w * 8, run = kw & ~63, off = kw & 63;   // two 4-input pieces, permuted inside their run of 64
         *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off)) = pk.x;
         *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off + 4)) = pk.y;
-        if ((w & (lpg - 1)) == 0) mrow[g] = mi;
+        if ((w & (lpg - 1)) == 0) mrow[g] = prm.fmt == RQ_FMT_E4M3 ? __float_as_int(__fmul_rn((float) mi, 0.0625f)) : mi;
     }
 }
 
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(ACT_THREADS) rq_act_cluster_kernel(const ActPa
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     build_sign_table(table, chi, P, tid, nt);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (t == 0 && rank == 0 && tid == 0 && prm.status != nullptr) *prm.status = 0;
+    if (t == 0 && rank == 0 && tid == 0 && prm.status != nullptr) { prm.status[0] = 0; prm.status[1] = prm.fmt; }
 
     // ---- Sylvester transform of this CTA's chunks (chunk rank + C*s lands in slot s)
     const float * xrow = prm.x + (int64_t) t * prm.ldx;
@@ -257,11 +258,11 @@ __global__ void __launch_bounds__(ACT_THREADS) rq_act_cluster_kernel(const ActPa
             float lo, hi;
             group_range(a, b, 8, prm.clip, lo, hi);
             int mi;
-            const uint2 pk = encode_word(a, b, lo, hi, R, unit, mi);
+            const uint2 pk = encode_word(a, b, lo, hi, R, unit, prm.fmt, mi);
             const int off = (w & 7) * 8;
             *reinterpret_cast<uint32_t *>(arow + kbase + rq_perm64(off)) = pk.x;
             *reinterpret_cast<uint32_t *>(arow + kbase + rq_perm64(off + 4)) = pk.y;
-            if ((w & 7) == 0) mrow[kbase >> 6] = mi;
+            if ((w & 7) == 0) mrow[kbase >> 6] = prm.fmt == RQ_FMT_E4M3 ? __float_as_int(__fmul_rn((float) mi, 0.0625f)) : mi;
         }
     }
 }
@@ -356,10 +357,10 @@ cudaError_t rq_configure_act() {
 }
 
 cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,
-                          float clip, int G, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,
+                          float clip, int G, int fmt, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,
                           int32_t * status, cudaStream_t stream) {
     ActParams prm;
-    prm.x = x; prm.ldx = ldx; prm.K = (int) K; prm.n_rot = n_rot; prm.p = p; prm.m = m; prm.G = G;
+    prm.x = x; prm.ldx = ldx; prm.K = (int) K; prm.n_rot = n_rot; prm.p = p; prm.m = m; prm.G = G; prm.fmt = fmt;
     prm.rot_scale = rot_scale; prm.clip = clip; prm.a8 = a8; prm.msh = msh; prm.u = u; prm.rot_out = rot_out; prm.ldo = ldo;
     prm.status = status;
     if (n_rot <= 0 || p == 1) return launch<1>(prm, M, stream);

@@ -204,8 +204,10 @@ __device__ __forceinline__ void group_range(const float4 a, const float4 b, int 
     hi = __fmul_rn(mx, clip);
 }
 
-// the 8 codes of a word as int8 8*(q - z) and the group's multiplier
-__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, int & mi) {
+// the 8 codes of a word and the group's multiplier.  fmt RQ_FMT_I8: int8 8*(q - z); RQ_FMT_E4M3: the e4m3 byte of
+// (q - z), exact, for the fp8 tensor-core path
+__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, int fmt,
+                                             int & mi) {
     const float mf = fminf(fmaxf(ceilf(__fdiv_rn(__fmul_rn(__fsub_rn(hi, lo), 255.0f), R)), 1.0f), 255.0f);
     mi = (int) mf;
     const float inv = __fdiv_rn(1.0f, __fmul_rn((float) mi, unit));
@@ -215,8 +217,9 @@ __device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, flo
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const float qf = fminf(fmaxf(__fadd_rn(rintf(__fmul_rn(v[j], inv)), zf), 0.0f), 15.0f);
-        const int d = RQ_ACT_SCALE * ((int) qf - (int) zf);   // 8*(q - z) in [-120, 120]
-        pk[j >> 2] |= (uint32_t) (d & 0xFF) << (8 * (j & 3));
+        const int dz = (int) qf - (int) zf;                                  // q - z in [-15, 15]
+        const uint32_t byte = fmt == RQ_FMT_E4M3 ? rq_e4m3_of_int(dz) : (uint32_t) ((RQ_ACT_SCALE * dz) & 0xFF);
+        pk[j >> 2] |= byte << (8 * (j & 3));
     }
     return make_uint2(pk[0], pk[1]);
 }

@@ -203,13 +203,14 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_rotate(const float
     int p = 0, m = 0;
     if (n_rot <= 0 || K % n_rot != 0 || !rq_hadamard_factor(n_rot, &p, &m)) return RQ_ERR_ROTATION;
     const float scale = 1.0f / sqrtf((float) n_rot);
-    RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, 1.0f, 64, nullptr, nullptr, nullptr, out_dev, ldo,
+    RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, 1.0f, 64, RQ_FMT_I8, nullptr, nullptr, nullptr, out_dev, ldo,
                           nullptr, (cudaStream_t) stream));
     return RQ_OK;
 }
 
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float clip,
-                                int act_group, void * workspace_dev, size_t workspace_bytes, void * stream) {
+                                int act_group, int act_format, void * workspace_dev, size_t workspace_bytes, void * stream) {
+    if (act_format != RQ_FMT_I8 && act_format != RQ_FMT_E4M3) return RQ_ERR_ARG;
     int rc = rq_check_x(x_dev, ldx, M, K);
     if (rc != RQ_OK) return rc;
     if (act_group != 64 && act_group != 128 && act_group != 256) return RQ_ERR_GROUP;
@@ -226,10 +227,34 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize(const flo
         return RQ_ERR_ROTATION;
     }
     uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
-    RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, clip, act_group, reinterpret_cast<int8_t *>(ws + l.off_a8),
+    RQ_CUDA(rq_launch_act(x_dev, ldx, M, K, (int) n_rot, p, m, scale, clip, act_group, act_format, reinterpret_cast<int8_t *>(ws + l.off_a8),
                           reinterpret_cast<int32_t *>(ws + l.off_msh), reinterpret_cast<float *>(ws + l.off_u), nullptr, 0,
                           reinterpret_cast<int32_t *>(ws + l.off_status), (cudaStream_t) stream));
     return RQ_OK;
+}
+
+// which kernel a weight takes at M tokens: true = tcgen05 GEMM, false = GEMV passes; -1 on a bad request
+static int rq_use_tc(const rq_weight_desc * w, int64_t M, int path) {
+    const bool has_dec = (w->layouts & RQ_PREPACK_DECODE) != 0, has_pre = (w->layouts & RQ_PREPACK_PREFILL) != 0;
+    if (path == RQ_PATH_GEMV) return has_dec ? 0 : -1;
+    if (path == RQ_PATH_TC) return has_pre ? 1 : -1;
+    // up to 64 tokens the GEMV in passes of 16 (the later passes read the stream from L2) beats a 128-token MMA tile
+    if (path == RQ_PATH_AUTO) return (has_pre && (M > 64 || !has_dec)) ? 1 : (has_dec ? 0 : -1);
+    return -1;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_act_format(const rq_weight_desc * const * w, int n_w, int64_t M, int path) {
+    if (w == nullptr || n_w < 1 || n_w > RQ_MAX_WEIGHTS) return RQ_ERR_ARG;
+    int fmt = -1;
+    for (int i = 0; i < n_w; ++i) {
+        if (w[i] == nullptr) return RQ_ERR_ARG;
+        const int tc = rq_use_tc(w[i], M, path);
+        if (tc < 0) return RQ_ERR_ARG;
+        const int f = (tc && !w[i]->wk_mode) ? RQ_FMT_E4M3 : RQ_FMT_I8;
+        if (fmt >= 0 && f != fmt) return RQ_ERR_MISMATCH;   // one activation cannot serve both formats
+        fmt = f;
+    }
+    return fmt;
 }
 
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(const rq_weight_desc * w, int64_t M, float * y_dev, int64_t ldy, int act_group,
@@ -247,16 +272,12 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(
     const int32_t * msh = reinterpret_cast<const int32_t *>(ws + l.off_msh);
     const float * u = reinterpret_cast<const float *>(ws + l.off_u);
     const float * sw = reinterpret_cast<const float *>(pp + w->off_sw);
-    const bool has_dec = (w->layouts & RQ_PREPACK_DECODE) != 0, has_pre = (w->layouts & RQ_PREPACK_PREFILL) != 0;
-    bool tc;
-    if (path == RQ_PATH_GEMV) { if (!has_dec) return RQ_ERR_ARG; tc = false; }
-    else if (path == RQ_PATH_TC) { if (!has_pre) return RQ_ERR_ARG; tc = true; }
-    // up to 64 tokens the GEMV in passes of 16 (the later passes read the stream from L2) beats a 128-token MMA tile
-    else if (path == RQ_PATH_AUTO) tc = has_pre && (M > 64 || !has_dec);
-    else return RQ_ERR_ARG;
+    const int use_tc = rq_use_tc(w, M, path);
+    if (use_tc < 0) return RQ_ERR_ARG;
+    const bool tc = use_tc != 0;
     int32_t * status = reinterpret_cast<int32_t *>(const_cast<uint8_t *>(ws) + l.off_status);
     if (tc) {
-        RQ_CUDA(rq_launch_gemm_tc(w->tmap_w8, sw, w->wk_mode, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
+        RQ_CUDA(rq_launch_gemm_tc(w->tmap_w8, sw, w->wk_mode ? RQ_FMT_I8 : RQ_FMT_E4M3, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
     } else {
         rq_gemv_job job;
         job.w4 = pp + w->off_w4; job.sw = sw; job.N = w->N; job.y = y_dev; job.ldy = ldy;
@@ -317,7 +338,9 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat(const rq_w
         // one activation serves all: same input width, type and rotation (ggml_cuda_rq_w4a4_can_fuse, patch:2394-2397)
         if (w[i]->K != w[0]->K || w[i]->type != w[0]->type || w[i]->n_rot != w[0]->n_rot) return RQ_ERR_MISMATCH;
     }
-    int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group,
+    const int fmt = rq_w4a4_act_format(w, n_w, M, path);
+    if (fmt < 0) return fmt;
+    int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group, fmt,
                               workspace_dev, workspace_bytes, stream);
     if (rc != RQ_OK) return rc;
     return rq_w4a4_mul_mat_quantized_n(w, n_w, M, y_dev, ldy, act_group, path, workspace_dev, workspace_bytes, stream);
@@ -331,5 +354,6 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_device_status(void
     RQ_CUDA(cudaMemcpyAsync(&st, static_cast<uint8_t *>(workspace_dev) + l.off_status, 4, cudaMemcpyDeviceToHost,
                             (cudaStream_t) stream));
     RQ_CUDA(cudaStreamSynchronize((cudaStream_t) stream));
-    return st ? RQ_ERR_DEVICE : RQ_OK;
+    // 1: a bounded wait expired; 2: the activation was quantized in the other kernel's format
+    return st == 0 ? RQ_OK : st == 2 ? RQ_ERR_MISMATCH : RQ_ERR_DEVICE;
 }

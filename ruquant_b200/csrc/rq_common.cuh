@@ -35,6 +35,14 @@ __host__ __device__ inline int rq_wmult(int32_t sum, int g) {
 __host__ __device__ inline int rq_perm64(int k4) {   // k4: offset of a 4-input piece inside the run (multiple of 4)
     return ((k4 & 15) >> 2) * 16 + (k4 >> 4) * 4;
 }
+// e4m3 byte of a small integer (|v| <= 15: at most four significant bits, so the conversion is exact)
+__host__ __device__ inline uint32_t rq_e4m3_of_int(int v) {
+    const uint32_t sign = v < 0 ? 0x80u : 0u;
+    const uint32_t a = (uint32_t) (v < 0 ? -v : v);
+    if (a == 0) return 0u;
+    const int e = a >= 8 ? 3 : a >= 4 ? 2 : a >= 2 ? 1 : 0;
+    return sign | (uint32_t) ((e + 7) << 3) | ((a << (3 - e)) & 7u);
+}
 #define RQ_ACT_SCALE 8     // activations are stored as 8*(q - z), |.| <= 120
 #define RQ_W_SCALE   16    // weights with multiplier 1 are stored as 16*c, in [-128, 112]
 
@@ -55,7 +63,7 @@ static inline rq_ws_layout rq_ws(int64_t K, int64_t M) {
 
 // Launchers (one per .cu file).  All enqueue on `stream` and return a cudaError_t.
 cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,
-                          float clip, int G, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,
+                          float clip, int G, int fmt, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,
                           int32_t * status, cudaStream_t stream);
 cudaError_t rq_launch_prepack(const rq_block * blocks, int64_t K, int64_t N, float * sw, uint8_t * w4, int8_t * w8,
                               int8_t * wk, int wk_mode, cudaStream_t stream);
@@ -71,7 +79,7 @@ struct rq_gemv_job {
 };
 cudaError_t rq_launch_gemv(const rq_gemv_job * jobs, int n_jobs, int64_t K, const int8_t * a8, const int32_t * msh,
                            const float * u, int64_t M, int G, int32_t * status, cudaStream_t stream);
-cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mode, int64_t K, int64_t N,
+cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
 // per-device kernel attributes (large dynamic shared memory); called from rq_w4a4_prepare so that the first

@@ -73,10 +73,16 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
 // instruction descriptor, kind::i8: D = s32 (2 at [4,6)), A and B signed int8 (1 at [7,10) and [10,13)), both
 // K-major (0 at 15, 16), N >> 3 at [17,23), M >> 4 at [24,29)
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
+// kind::f8f6f4: D = f32 (1 at [4,6)), A and B e4m3 (0 at [7,10) and [10,13)), K-major, same N and M fields
+constexpr uint32_t IDESC_F8 = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
 
 __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                  :: "r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(da), "l"(db), "r"(IDESC_F8), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
@@ -108,12 +114,37 @@ __device__ __forceinline__ void tmem_ld_wait(int (&v)[32]) {
 
 // one integer multiply and one shift-add per output per group (measured on B200: 50+ outputs per clock per SM,
 // against 30 for a high multiply-add)
-template <bool WK>
+// integer path (weights k*c, activations 8*(q - z)): D = 8*k*S, term = (D * m) >> 7
 __device__ __forceinline__ void fold32(int (&tot)[128], int base, const int (&v)[32], int mm) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        if (WK) tot[base + i] += (v[i] * mm) >> 7;
-        else    tot[base + i] += (v[i] * mm) >> RQ_FOLD_SHIFT;
+    for (int i = 0; i < 32; ++i) tot[base + i] += (v[i] * mm) >> 7;
+}
+
+// fp8 path: D = S exactly (fp32 accumulation of products of small integers).  The running total lives in a float
+// kept inside [2^23, 2^24), where the spacing of floats is 1: a round-down fused multiply-add
+//     t <- fma.rm(S, m/16, t)
+// adds floor(S*m/16) = (m*S) >> 4 exactly (S*m/16 has at most 21 + 4 significant bits below 2^23, the sum is rounded
+// once, downwards, to an integer) -- the reference's shifted term in ONE instruction at the full fp32 rate.
+constexpr float FOLD_MAGIC = 12582912.0f;        // 1.5 * 2^23
+constexpr int FOLD_MAGIC_BITS = 0x4B400000;
+__device__ __forceinline__ float fma_rm(float a, float b, float c) {
+    float d;
+    asm("fma.rm.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void fold32_f8(float (&tf)[128], int base, const int (&v)[32], float mf) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) tf[base + i] = fma_rm(__int_as_float(v[i]), mf, tf[base + i]);
+}
+// Every 1024 inputs the float is re-centred: what it holds above +-2^19 moves, in units of 2^20, into a signed byte
+// of a packed carry word (at most 32 re-centrings of at most +-3 each), so the float never leaves its window.
+__device__ __forceinline__ void recenter(float (&tf)[128], int (&carry)[32]) {
+#pragma unroll
+    for (int i = 0; i < 128; ++i) {
+        const int k = __float_as_int(tf[i]) - FOLD_MAGIC_BITS;
+        const int c = (k + (1 << 19)) >> 20;
+        tf[i] = __int_as_float(FOLD_MAGIC_BITS + (k - (c << 20)));
+        carry[i >> 2] += c << (8 * (i & 3));
     }
 }
 
@@ -133,8 +164,9 @@ struct __align__(8) TcShared {
     int abort_flag;
 };
 
-// WK = false: multipliers all 1, B holds 16*c.  WK = true: B holds k*c.
-template <bool WK>
+// F8 = true: multipliers all 1, operands are e4m3 bytes of c and (q - z), fp8 MMA with fp32 accumulators, float fold.
+// F8 = false: weight multipliers present, B holds int8 k*c, A int8 8*(q - z), integer MMA and integer fold.
+template <bool F8>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams prm) {
     extern __shared__ uint8_t smem_raw[];
@@ -207,7 +239,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
                     for (int kk = 0; kk < 2; ++kk) {
                         const uint32_t koff = (uint32_t) ((h * 64 + kk * 32) >> 4);   // bytes >> 4 inside the swizzled row
-                        umma_i8(d, da + koff, db + koff, (gs | kk) != 0 ? 1u : 0u);
+                        if (F8) umma_f8(d, da + koff, db + koff, (gs | kk) != 0 ? 1u : 0u);
+                        else    umma_i8(d, da + koff, db + koff, (gs | kk) != 0 ? 1u : 0u);
                     }
                     if (gs == gsteps - 1) umma_commit(smem_u32(&sh.tmem_full[buf]));
                 }
@@ -216,15 +249,28 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
     }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
         const int e = warp - 4, quarter = warp & 3, half = e >> 2;
         const int row = m_tile * BM + quarter * 32 + lane;
         const bool row_ok = row < prm.M;
         const uint32_t lane_base = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (half * 128);
         const int32_t * mrow = prm.msh + (size_t) (row_ok ? row : 0) * n_ag;
-        int tot[128];
+        // the quantizer records the format it wrote: refuse to multiply the wrong one
+        const bool fmt_ok = prm.status == nullptr || prm.status[1] == (F8 ? RQ_FMT_E4M3 : RQ_FMT_I8);
+        int tot[F8 ? 1 : 128];
+        float tf[F8 ? 128 : 1];
+        int carry[F8 ? 32 : 1];
+        if (F8) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) tot[i] = 0;
+            for (int i = 0; i < 128; ++i) tf[F8 ? i : 0] = FOLD_MAGIC;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) carry[F8 ? i : 0] = 0;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 128; ++i) tot[F8 ? 0 : i] = 0;
+        }
+        const int recenter_every = prm.G >= 1024 ? 1 : 1024 / prm.G;
+        int since = 0;
         int mnext = row_ok ? __ldg(mrow) : 0;
         bool ok = true;
         for (int ag = 0; ag < n_ag; ++ag) {
@@ -235,23 +281,44 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_full[buf]), (ag >> 1) & 1, abort_flag))) { ok = false; break; }
             tc_fence_after();
             const uint32_t t0 = lane_base + (uint32_t) buf * BN;
-            // software pipeline over the four 32-column chunks: the load of chunk c+1 is in flight while chunk c folds
-            int va[32], vb[32];
-            tmem_ld32(t0, va);
-            tmem_ld_wait(va);
-            tmem_ld32(t0 + 32, vb);
-            fold32<WK>(tot, 0, va, mm);
-            tmem_ld_wait(vb);
-            tmem_ld32(t0 + 64, va);
-            fold32<WK>(tot, 32, vb, mm);
-            tmem_ld_wait(va);
-            tmem_ld32(t0 + 96, vb);
-            fold32<WK>(tot, 64, va, mm);
-            tmem_ld_wait(vb);
-            fold32<WK>(tot, 96, vb, mm);
+            if constexpr (F8) {
+                const float mf = __int_as_float(mm);          // m / 16
+                int va[32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld32(t0 + c * 32, va);
+                    tmem_ld_wait(va);
+                    if (c == 0) fold32_f8(tf, 0, va, mf);
+                    else if (c == 1) fold32_f8(tf, 32, va, mf);
+                    else if (c == 2) fold32_f8(tf, 64, va, mf);
+                    else fold32_f8(tf, 96, va, mf);
+                }
+            } else {
+                // software pipeline over the four 32-column chunks: the load of chunk c+1 is in flight while chunk c folds
+                int va[32], vb[32];
+                tmem_ld32(t0, va);
+                tmem_ld_wait(va);
+                tmem_ld32(t0 + 32, vb);
+                fold32(tot, 0, va, mm);
+                tmem_ld_wait(vb);
+                tmem_ld32(t0 + 64, va);
+                fold32(tot, 32, vb, mm);
+                tmem_ld_wait(va);
+                tmem_ld32(t0 + 96, vb);
+                fold32(tot, 64, va, mm);
+                tmem_ld_wait(vb);
+                fold32(tot, 96, vb, mm);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[buf]));
+            if constexpr (F8) {
+                if (++since == recenter_every || ag == n_ag - 1) { recenter(tf, carry); since = 0; }
+            }
+        }
+        if (!fmt_ok) {
+            ok = false;
+            if (lane == 0 && prm.status != nullptr) atomicExch(prm.status, 2);
         }
         if (ok && row_ok) {
             const float ut = __ldg(prm.u + row);
@@ -261,11 +328,20 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
             for (int i = 0; i < 128; i += 4) {
                 float f[4];
+                int P = F8 ? carry[F8 ? i >> 2 : 0] : 0;      // four signed byte digits, units of 2^20
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int n = n0 + i + j;
                     const float s = n < prm.N ? __ldg(prm.sw + n) : 0.0f;
-                    f[j] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[i + j], 16.0f), ut), s);
+                    int total;
+                    if (F8) {
+                        const int d = (int) (signed char) (P & 0xFF);
+                        total = d * (1 << 20) + (__float_as_int(tf[F8 ? i + j : 0]) - FOLD_MAGIC_BITS);
+                        P = (P - d) >> 8;
+                    } else {
+                        total = tot[F8 ? 0 : i + j];
+                    }
+                    f[j] = __fmul_rn(__fmul_rn(__fmul_rn((float) total, 16.0f), ut), s);
                 }
                 if (vec && n0 + i + 3 < prm.N) {
                     *reinterpret_cast<float4 *>(yr + n0 + i) = make_float4(f[0], f[1], f[2], f[3]);
@@ -322,12 +398,13 @@ int rq_encode_tmap_i8(void * tmap_out, const void * base, int64_t K, int64_t row
 }
 
 cudaError_t rq_configure_gemm_tc() {
+    // <true>: fp8 operands (no weight multipliers); <false>: int8 operands
     cudaError_t e = cudaFuncSetAttribute(rq_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(rq_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
 }
 
-cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mode, int64_t K, int64_t N,
+cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream) {
     static bool configured[64] = {};
@@ -346,7 +423,7 @@ cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int wk_mod
     prm.sw = sw; prm.msh = msh; prm.u = u; prm.y = y; prm.ldy = ldy; prm.status = status;
     prm.K = (int) K; prm.N = (int) N; prm.M = (int) M; prm.G = G;
     const dim3 grid((unsigned) ((M + BM - 1) / BM), (unsigned) ((N + BN - 1) / BN));
-    if (wk_mode) rq_gemm_tc_kernel<true><<<grid, TC_THREADS, SMEM_BYTES, stream>>>(ta, tb, prm);
-    else         rq_gemm_tc_kernel<false><<<grid, TC_THREADS, SMEM_BYTES, stream>>>(ta, tb, prm);
+    if (fmt == RQ_FMT_E4M3) rq_gemm_tc_kernel<true><<<grid, TC_THREADS, SMEM_BYTES, stream>>>(ta, tb, prm);
+    else                    rq_gemm_tc_kernel<false><<<grid, TC_THREADS, SMEM_BYTES, stream>>>(ta, tb, prm);
     return cudaGetLastError();
 }

@@ -149,6 +149,8 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 
     // ---- consumers.  Everything below reads what the preceding kernel (the quantizer) wrote.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // this kernel multiplies int8 activations; one quantized for the fp8 tensor-core path is refused (status 2, no stores)
+    const bool fmt_ok = prm.status == nullptr || prm.status[1] == RQ_FMT_I8;
 
     // B fragments: token gid (+8 for the second tile); the quantizer stores each run of 64 inputs so that the 16
     // bytes at offset tig*16 are inputs {0,16,32,48} + tig*4 .. +3: b0, b1 of both MMAs in one 128-bit load.
@@ -293,6 +295,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                 for (int w = 0; w < CONSUMERS; ++w) v += pt[(w * 32 + lane) * 4 * NT + t * 4 + i];
                 tot[t][i] = v;
             }
+        if (!fmt_ok && lane == 0) atomicExch(prm.status, 2);
         const float s_lo = row_lo < jb.N ? __ldg(jb.sw + row_lo) : 0.0f;
         const float s_hi = row_hi < jb.N ? __ldg(jb.sw + row_hi) : 0.0f;
 #pragma unroll
@@ -300,7 +303,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int tok = 8 * t + 2 * tig + c;
-                if (tok < M) {
+                if (tok < M && fmt_ok) {
                     const float ut = __ldg(prm.u + tok);
                     if (row_lo < jb.N) jb.y[(size_t) tok * jb.ldy + row_lo] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][c], 16.0f), ut), s_lo);
                     if (row_hi < jb.N) jb.y[(size_t) tok * jb.ldy + row_hi] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][2 + c], 16.0f), ut), s_hi);

@@ -9,7 +9,8 @@
 //                      tile*16 + gid + 8, inputs run*64 + (j/2)*32 + (j%2)*16 + tig*4 .. +3 -- exactly the A fragment
 //                      of mma.m16n8k32 (a nibble moved to the top of its byte is 16*c in two's complement: no sign
 //                      fix-up).  Rows beyond N are zero.
-//   w8  i8  [N][K]     tensor-core operand: 16*c when every multiplier is 1, else k*c (|k*c| <= 120), permuted
+//   w8  u8  [N][K]     tensor-core operand: the e4m3 byte of c when every multiplier is 1 (fp8 MMA, fp32 accumulate,
+//                      exact on these integers), else int8 k*c (|k*c| <= 120, integer MMA), permuted
 //                      inside each run of 64 inputs like the activations (rq_perm64)
 //   wk  i8  [N][K/64]  the multiplier of each run of 64 inputs (RQ_W_MULT_G, patch:40-43), only when some k != 1
 #include "rq_common.cuh"
@@ -39,12 +40,13 @@ __global__ void rq_prepack_kernel(const rq_block * __restrict__ blocks, int64_t 
     if (w == 0) sw[row] = b->d;
     if (wk != nullptr && (w % 8) == 0) wk[row * (K / 64) + w / 8] = (int8_t) k;
     if (w8 != nullptr) {
-        const int mult = wk_mode ? k : RQ_W_SCALE;
         uint32_t pk[2] = { 0u, 0u };
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int c = ((int) (((src >> (4 * j)) & 0xFu) << 28)) >> 28;
-            pk[j >> 2] |= (uint32_t) ((c * mult) & 0xFF) << (8 * (j & 3));
+            // multipliers present: int8 k*c for the integer MMA; else the e4m3 byte of c (|c| <= 8, exact) for the fp8 MMA
+            const uint32_t byte = wk_mode ? (uint32_t) ((c * k) & 0xFF) : rq_e4m3_of_int(c);
+            pk[j >> 2] |= byte << (8 * (j & 3));
         }
         const int64_t kw = w * 8, run = kw & ~(int64_t) 63;
         const int off = (int) (kw & 63);                     // same permutation as the activations (rq_perm64)

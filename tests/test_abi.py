@@ -62,5 +62,5 @@ def test_null_arguments_return_status_not_crash(lib):
     # error behaviour: status codes where the reference aborts
     assert lib.rq_w4a4_prepare(None, 44, 4096, 64, None, 0, 3, None, None) == -1
     assert lib.rq_w4a4_mul_mat(None, 1, None, 0, 1, None, None, 1.0, 64, 0, None, 0, None) == -1
-    assert lib.rq_w4a4_quantize(None, 4096, 1, 4096, 0, 1.0, 64, None, 0, None) == -1
+    assert lib.rq_w4a4_quantize(None, 4096, 1, 4096, 0, 1.0, 64, 0, None, 0, None) == -1
     assert lib.rq_w4a4_rotate(None, 4096, 1, 4096, 4096, None, 4096, None) == -1

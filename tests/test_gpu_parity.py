@@ -85,6 +85,48 @@ def test_activation_quantizer_fields(rq, port, group):
         assert (got == want).all(), "codes"
 
 
+def _e4m3_value(b):
+    """Value of an e4m3 byte (no NaN/inf codes occur for |v| <= 15)."""
+    b = b.astype(np.int32)
+    e, mant = (b >> 3) & 15, b & 7
+    mag = np.where(e == 0, mant / 8.0 * 2.0 ** -6, (1 + mant / 8.0) * 2.0 ** (e - 7))
+    return np.where(b & 0x80, -mag, mag)
+
+
+def test_activation_quantizer_e4m3_format(rq, port):
+    """The tcgen05 fp8 path's activation: bytes are e4m3 of (q - z), multipliers are float bits of m/16."""
+    for K, n_rot, clip, group in [(4096, 0, 1.0, 64), (5120, 5120, 0.9, 128), (2048, 2048, 0.8, 256)]:
+        x = inputs.outlier_activations(3, K, 12)
+        x[1] = 0.0
+        ws, a8, msh, u = rq.quantize(dev(x), n_rot, clip, group, fmt=rq.FMT_E4M3)
+        torch.cuda.synchronize()
+        uo, mo, zo, qo = oracle.act_fields(port.quantize_act(x, clip, group, n_rot), group)
+        assert_bits(u.cpu().numpy(), uo, "unit")
+        assert_bits(msh.cpu().numpy().view(np.float32), (mo / 16.0).astype(np.float32), "multipliers")
+        want = qo - np.repeat(zo, group, axis=1)
+        k = np.arange(K)
+        off = k % 64
+        pos = (k - off) + ((off % 16) // 4) * 16 + (off // 16) * 4 + off % 4
+        got = _e4m3_value(a8.cpu().numpy().view(np.uint8)[:, pos])
+        assert (got == want).all(), "codes"
+
+
+def test_activation_format_mismatch_is_refused(rq, port):
+    K, N = 1024, 48
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 130), 44)
+    w = rq.Weight(dev(wb).view(-1), 44, K, N=N)
+    assert rq.act_format(w, 4, rq.PATH_GEMV) == rq.FMT_I8 and rq.act_format(w, 4, rq.PATH_TC) == rq.FMT_E4M3
+    x = dev(inputs.outlier_activations(4, K, 131))
+    y = torch.full((4, N), 7.0, dtype=torch.float32, device="cuda")
+    for fmt, path in [(rq.FMT_E4M3, rq.PATH_GEMV), (rq.FMT_I8, rq.PATH_TC)]:
+        ws, *_ = rq.quantize(x, 0, 1.0, 64, fmt=fmt)
+        rq.mul_mat_quantized(w, 4, ws, out=y, act_group=64, path=path)
+        with pytest.raises(rq.RqError) as e:
+            rq.device_status(ws, K, 4)
+        assert e.value.status == -7
+        assert (y == 7.0).all()           # nothing was stored
+
+
 # ------------------------------------------------------------------------------------------- golden MUL_MAT
 
 @pytest.mark.parametrize("path", [1, 2], ids=["gemv", "tcgen05"])
