@@ -9,7 +9,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "librq_b200.so")
+LIB_PATH = os.environ.get("RQ_B200_LIB") or os.path.join(HERE, "librq_b200.so")
 
 TYPE_W4A4, TYPE_W4A4H = 44, 45
 BLOCK_CODES, BLOCK_BYTES = 256, 144

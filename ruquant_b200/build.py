@@ -1,6 +1,9 @@
 """Builds ruquant_b200/librq_b200.so (the C-ABI library of include/rq_b200.h) with nvcc for sm_100a, in-tree.
 
-    python -m ruquant_b200.build [--force]
+    python -m ruquant_b200.build [--force] [-v]
+
+RQ_NVCC_EXTRA in the environment adds compiler flags (e.g. -DRQ_TRACE for the kernels' timeline diagnostics);
+RQ_B200_LIB names another output file (the package loads the same variable), for side-by-side builds.
 
 nvcc cross-compiles without a GPU.  The library links the CUDA runtime statically and has no other dependency
 (no torch, no libcuda at link time: the one driver entry point it needs is fetched through the runtime).
@@ -11,7 +14,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.path.join(HERE, "librq_b200.so")
+LIB = os.environ.get("RQ_B200_LIB") or os.path.join(HERE, "librq_b200.so")
 SOURCES = ["rq_api.cu", "rq_act.cu", "rq_prepack.cu", "rq_gemv.cu", "rq_gemm_tc.cu", "rq_static.cu", "rq_ggml_adapter.cu"]
 NVCC_FLAGS = ["-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-cudart", "static"]
@@ -35,8 +38,9 @@ def build(force=False, verbose=False):
         path = os.path.join(CSRC, src)
         if not os.path.exists(path):
             continue
-        obj = os.path.join(CSRC, src[:-3] + ".o")
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
+        obj = os.path.join(CSRC, src[:-3] + (".o" if not os.environ.get("RQ_B200_LIB") else "." + os.path.basename(LIB) + ".o"))
+        cmd = ([nvcc] + NVCC_FLAGS + os.environ.get("RQ_NVCC_EXTRA", "").split() + (["-Xptxas", "-v"] if verbose else [])
+               + ["-c", path, "-o", obj])
         procs.append((cmd, subprocess.Popen(cmd)))
         objs.append(obj)
     for cmd, p in procs:

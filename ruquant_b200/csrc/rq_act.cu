@@ -22,6 +22,8 @@
 
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "rq_common.cuh"
 #include "rq_act_dev.cuh"
 
@@ -30,6 +32,8 @@ namespace cg = cooperative_groups;
 namespace {
 
 constexpr int ACT_THREADS = 256;
+// threads of a cluster CTA: a thread of the Paley stage keeps P inputs in registers
+constexpr int cluster_threads(int p) { return p <= 72 ? 512 : 256; }
 
 using namespace rq_act_dev;
 
@@ -61,13 +65,19 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
     float * table = buf + K;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    RQ_STAMP_DECL;
+    RQ_STAMP(tid == 0);                                     // 0: start
+    // pull the row towards L2 while the kernel ahead may still be running (a hint: no value is read before the wait)
+    for (int i = tid; i < K / 32; i += nt) asm volatile("prefetch.global.L2 [%0];" :: "l"(prm.x + (int64_t) t * prm.ldx + i * 32));
     if constexpr (P > 1) build_sign_table(table, chi, P, tid, nt);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (t == 0 && tid == 0 && prm.status != nullptr) { prm.status[0] = 0; prm.status[1] = prm.fmt; }
+    RQ_STAMP(tid == 0);                                     // 1: after the wait
 
     const float * xrow = prm.x + (int64_t) t * prm.ldx;
     if (prm.n_rot > 0) {
         load_fwht(xrow, buf, K, prm.m, tid, nt);
+        RQ_STAMP(tid == 0);                                 // 2: chunks transformed
     } else {
         for (int i = tid; i < K / 4; i += nt) reinterpret_cast<float4 *>(buf)[i] = __ldg(reinterpret_cast<const float4 *>(xrow) + i);
         __syncthreads();
@@ -100,6 +110,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
         }
     }
     if (prm.a8 == nullptr) return;
+    RQ_STAMP(tid == 0);                                     // 3: Paley done
 
     // ---- quantizer: a thread owns a word of 8 values, G/8 neighbouring lanes own a group
     const int lpg = prm.G >> 3, nwords = K >> 3;
@@ -113,130 +124,106 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
         }
         tmax = fmaxf(tmax, __fsub_rn(hi, lo));
     }
-    for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
-    if ((tid & 31) == 0) red[tid >> 5] = tmax;
+    tmax = cta_max_warp0(tmax, red, tid, nt);
+    if (tid == 0) red[0] = tmax;
     __syncthreads();
-    float R = 0.0f;
-    for (int i = 0; i < nt / 32; ++i) R = fmaxf(R, red[i]);
+    float R = red[0];
     if (R == 0.0f) R = 2.0f;
     const float unit = __fdiv_rn(R, 15.0f * 255.0f);
     if (tid == 0) prm.u[t] = unit;
+    RQ_STAMP(tid == 0);                                     // 4: ranges reduced
 
     int8_t * arow = prm.a8 + (int64_t) t * K;
     int32_t * mrow = prm.msh + (int64_t) t * (K / prm.G);
-    for (int w = tid; w < nwords; w += nt) {
-        const int g = w / lpg;
-        int mi;
-        const uint2 pk = encode_word(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1],
-                                     g_lo[g], g_hi[g], R, unit, prm.fmt, mi);
-        const int kw = w * 8, run = kw & ~63, off = kw & 63;   // two 4-input pieces, permuted inside their run of 64
-        *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off)) = pk.x;
-        *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off + 4)) = pk.y;
-        if ((w & (lpg - 1)) == 0) mrow[g] = prm.fmt == RQ_FMT_E4M3 ? __float_as_int(__fmul_rn((float) mi, 0.0625f)) : mi;
-    }
+    auto store_codes = [&](auto f8) {
+        constexpr bool F8 = decltype(f8)::value;
+        for (int w = tid; w < nwords; w += nt) {
+            const int g = w / lpg;
+            int mi;
+            const uint2 pk = encode_word<F8>(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1],
+                                             g_lo[g], g_hi[g], R, unit, mi);
+            const int kw = w * 8, run = kw & ~63, off = kw & 63;   // two 4-input pieces, permuted inside their run of 64
+            *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off)) = pk.x;
+            *reinterpret_cast<uint32_t *>(arow + run + rq_perm64(off + 4)) = pk.y;
+            if ((w & (lpg - 1)) == 0) mrow[g] = multiplier_word<F8>(mi);
+        }
+    };
+    if (prm.fmt == RQ_FMT_E4M3) store_codes(std::true_type{});
+    else store_codes(std::false_type{});
+    RQ_STAMP(tid == 0);                                     // 5: codes stored
+    RQ_STAMP_FLUSH(tid == 0, prm.status, 0x30);
 }
 
 // =====================================================================================  a cluster per token
-// For G = 64, m a multiple of 64 and P > 1.  C = gridDim.x CTAs per token (8 or a smaller power of two).
-//   chunk ch = blk * P + i (m floats) is loaded and transformed by CTA ch % C into its slot ch / C;
-//   slice sl = blk * (m/64) + js owns columns [64 js, 64 js + 64) of block blk; T = K / (64 P) slices.
-//   With C >= T, cps = C / T CTAs share a slice and deal its NB = P / 4 blocks of 4 outputs round-robin; with C < T a
-//   CTA walks nsl = T / C slices and forms all their outputs.  Per slice the CTA first copies the slice's P x 64
-//   inputs out of the owners' shared memory (distributed shared memory, 256-byte rows), then a thread = (column,
-//   block slot) forms 4 outputs from registers; a row of 64 outputs is one activation group.
-// shared memory: [slots * m chunks][P*P sign table][P * 64 slice][nsl * nb_max * 4 * 64 outputs]
-template <int P>
-__global__ void __launch_bounds__(ACT_THREADS) rq_act_cluster_kernel(const ActParams prm, int slots, int cps, int nsl, int nb_max) {
+// For G = 64, m a multiple of 64 and P > 1: decode widths, where one SM is too slow and every hand-over between CTAs
+// costs about as much as a whole phase.  C = gridDim.x CTAs per token.  Every CTA loads the whole row and transforms
+// all its chunks (cheap, and it spares a cluster barrier and a gather through distributed shared memory); the Paley
+// outputs are dealt out in units of 4 output chunks x 64 columns -- unit v = (blk * (m/64) + js) * (P/4) + ab covers
+// outputs blk*n + (4 ab + k)*m + 64 js + col, k < 4, col < 64: four activation groups -- round-robin, unit v to CTA
+// v % C.  A thread = (column, unit slot) forms the unit's 4 outputs of its column from registers.  The only exchange
+// is the token's range: one float per CTA written into every peer's shared memory, one cluster barrier.
+// shared memory: [K row][P*P sign table][units_max * 4 * 64 outputs]
+template <int P, int THREADS>
+__global__ void __launch_bounds__(THREADS) rq_act_cluster_kernel(const ActParams prm, int units_max) {
     extern __shared__ __align__(16) float smem[];
-    __shared__ float red[ACT_THREADS / 32];
-    __shared__ float peer_max[8];
+    __shared__ float red[THREADS / 32];
+    __shared__ float peer_max[16];
     __shared__ signed char chi[128];
     cg::cluster_group cluster = cg::this_cluster();
-    const int C = gridDim.x, rank = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
+    const int C = gridDim.x, rank = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, nt = THREADS;
     const int K = prm.K, m = prm.m, n = prm.n_rot;
-    const int nchunks = K / m, spb = m / 64, NB = P / 4;
-    float * chunks = smem;
-    float * table = chunks + (size_t) slots * m;
-    float * slice = table + P * P;
-    float * outs = slice + P * 64;
+    constexpr int NB = P / 4;
+    const int nq = m >> 6, units = (K / n) * nq * NB;
+    const int nl = (units - rank + C - 1) / C;              // units of this CTA: rank, rank + C, ...
+    float * row = smem;
+    float * table = row + K;
+    float * outs = table + P * P;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    RQ_STAMP_DECL;
+    RQ_STAMP(tid == 0);                                     // 0: start
+    // pull the row towards L2 while the kernel ahead may still be running (a hint: no value is read before the wait)
+    for (int i = rank * nt + tid; i < K / 32; i += C * nt) asm volatile("prefetch.global.L2 [%0];" :: "l"(prm.x + (int64_t) t * prm.ldx + i * 32));
     build_sign_table(table, chi, P, tid, nt);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    RQ_STAMP(tid == 0);                                     // 1: after the wait
     if (t == 0 && rank == 0 && tid == 0 && prm.status != nullptr) { prm.status[0] = 0; prm.status[1] = prm.fmt; }
 
-    // ---- Sylvester transform of this CTA's chunks (chunk rank + C*s lands in slot s)
-    const float * xrow = prm.x + (int64_t) t * prm.ldx;
-    {
-        int nloc = 0;
-        for (int ch = rank; ch < nchunks; ch += C) ++nloc;
-        switch (m < 1024 ? m : 1024) {
-            case 64:   cluster_chunks<2>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
-            case 128:  cluster_chunks<4>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
-            case 256:  cluster_chunks<8>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
-            case 512:  cluster_chunks<16>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
-            default:   cluster_chunks<32>(xrow, chunks, rank, C, nloc, m, tid, nt); break;
-        }
-        __syncthreads();
-        for (int ls = 10; (1 << ls) < m; ls += 3) {
-            const int rem = m >> ls;
-            if (rem >= 8) fwht_pass<8>(chunks, nloc * m, ls, tid, nt);
-            else if (rem == 4) fwht_pass<4>(chunks, nloc * m, ls, tid, nt);
-            else fwht_pass<2>(chunks, nloc * m, ls, tid, nt);
-            __syncthreads();
-        }
-    }
-    cluster.sync();
+    // ---- Sylvester transform of every chunk of the row
+    load_fwht(prm.x + (int64_t) t * prm.ldx, row, K, m, tid, nt);
+    RQ_STAMP(tid == 0);                                     // 2: chunks transformed
 
-    // ---- Paley, slice by slice
-    const int col = tid & 63, bslot = tid >> 6;            // 4 block slots run side by side
-    const int sub = C >= (K / (64 * P)) ? rank % cps : 0;
-    float tmax = 0.0f;
-    for (int si = 0; si < nsl; ++si) {
-        const int sl = cps > 1 || nsl == 1 ? rank / cps : rank + si * C;
-        const int blk = sl / spb, js = sl - blk * spb;
-        for (int idx = tid; idx < P * 16; idx += nt) {      // the slice's P rows of 64 floats, as float4
-            const int i = idx >> 4, q4 = idx & 15;
-            const int ch = blk * P + i;
-            const float * remote = cluster.map_shared_rank(chunks, ch % C);
-            reinterpret_cast<float4 *>(slice)[idx] = *reinterpret_cast<const float4 *>(remote + (size_t) (ch / C) * m + js * 64 + q4 * 4);
-        }
-        __syncthreads();
+    // ---- Paley: this CTA's units, THREADS / 64 of them side by side
+    const int col = tid & 63;
+    for (int l = tid >> 6; l < nl; l += THREADS / 64) {
+        const int v = rank + l * C;
+        const int ab = v % NB, sl = v / NB, js = sl % nq, blk = sl / nq;
+        const float * b = row + (size_t) blk * n + js * 64 + col;
         float colv[P];
 #pragma unroll
-        for (int i = 0; i < P; ++i) colv[i] = slice[i * 64 + col];
-        for (int lb = bslot; lb * cps + sub < NB; lb += 4) {
-            const int ab = lb * cps + sub;
-            float out[4];
-            paley_block4<P>(colv, table, ab * 4, prm.rot_scale, out);
+        for (int i = 0; i < P; ++i) colv[i] = b[i * m];
+        float out[4];
+        paley_block4<P>(colv, table, ab * 4, prm.rot_scale, out);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) outs[((si * nb_max + lb) * 4 + k) * 64 + col] = out[k];
-        }
-        __syncthreads();
+        for (int k = 0; k < 4; ++k) outs[(l * 4 + k) * 64 + col] = out[k];
     }
-
-    // ---- group ranges: a row of 64 outputs is one activation group (8 lanes x 8 values)
-    int my_nb = 0;
-    for (int ab = sub; ab < NB; ab += cps) ++my_nb;
-    const int words_per_slice = my_nb * 32;                 // 4 rows x 8 words per block
-    for (int si = 0; si < nsl; ++si) {
-        for (int w = tid; w < words_per_slice; w += nt) {
-            const int wi = (si * nb_max * 4) * 8 + w;
-            float lo, hi;
-            group_range(reinterpret_cast<float4 *>(outs)[2 * wi], reinterpret_cast<float4 *>(outs)[2 * wi + 1], 8, prm.clip, lo, hi);
-            tmax = fmaxf(tmax, __fsub_rn(hi, lo));
-        }
-    }
-    for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
-    if ((tid & 31) == 0) red[tid >> 5] = tmax;
     __syncthreads();
-    if (tid < C) {
-        float v = 0.0f;
-        for (int i = 0; i < nt / 32; ++i) v = fmaxf(v, red[i]);
-        float * remote = cluster.map_shared_rank(peer_max, tid);   // my maximum into slot `rank` of CTA tid
-        remote[rank] = v;
+    RQ_STAMP(tid == 0);                                     // 3: Paley done
+
+    // ---- group ranges: a row of 64 outputs is one activation group (8 lanes x 8 values); nl * 32 words, so a warp is
+    // inside or outside the loop as a whole
+    const int words = nl * 32;
+    float tmax = 0.0f;
+    for (int w = tid; w < words; w += nt) {
+        float lo, hi;
+        group_range(reinterpret_cast<float4 *>(outs)[2 * w], reinterpret_cast<float4 *>(outs)[2 * w + 1], 8, prm.clip, lo, hi);
+        tmax = fmaxf(tmax, __fsub_rn(hi, lo));
     }
+    tmax = cta_max_warp0(tmax, red, tid, nt);
+    if (tid < C) cluster.map_shared_rank(peer_max, tid)[rank] = tmax;     // my maximum into slot `rank` of CTA tid
+    RQ_STAMP(tid == 0);                                     // 4: ranges reduced
     cluster.sync();
+    RQ_STAMP(tid == 0);                                     // 5: cluster barrier
     float R = 0.0f;
     for (int i = 0; i < C; ++i) R = fmaxf(R, peer_max[i]);
     if (R == 0.0f) R = 2.0f;
@@ -246,25 +233,28 @@ __global__ void __launch_bounds__(ACT_THREADS) rq_act_cluster_kernel(const ActPa
     // ---- codes
     int8_t * arow = prm.a8 + (int64_t) t * K;
     int32_t * mrow = prm.msh + (int64_t) t * (K / 64);
-    for (int si = 0; si < nsl; ++si) {
-        const int sl = cps > 1 || nsl == 1 ? rank / cps : rank + si * C;
-        const int blk = sl / spb, js = sl - blk * spb;
-        for (int w = tid; w < words_per_slice; w += nt) {
-            const int row = w >> 3, lb = row >> 2, k = row & 3;
-            const int ab = lb * cps + sub;
-            const int kbase = blk * n + (ab * 4 + k) * m + js * 64;      // first input of this group in the row
-            const int wi = (si * nb_max * 4) * 8 + w;
-            const float4 a = reinterpret_cast<float4 *>(outs)[2 * wi], b = reinterpret_cast<float4 *>(outs)[2 * wi + 1];
+    auto store_codes = [&](auto f8) {
+        constexpr bool F8 = decltype(f8)::value;
+        for (int w = tid; w < words; w += nt) {
+            const int r = w >> 3, l = r >> 2, k = r & 3;
+            const int v = rank + l * C;
+            const int ab = v % NB, sl = v / NB, js = sl % nq, blk = sl / nq;
+            const int kbase = blk * n + (ab * 4 + k) * m + js * 64;         // first input of this group in the row
+            const float4 a = reinterpret_cast<float4 *>(outs)[2 * w], b = reinterpret_cast<float4 *>(outs)[2 * w + 1];
             float lo, hi;
             group_range(a, b, 8, prm.clip, lo, hi);
             int mi;
-            const uint2 pk = encode_word(a, b, lo, hi, R, unit, prm.fmt, mi);
+            const uint2 pk = encode_word<F8>(a, b, lo, hi, R, unit, mi);
             const int off = (w & 7) * 8;
             *reinterpret_cast<uint32_t *>(arow + kbase + rq_perm64(off)) = pk.x;
             *reinterpret_cast<uint32_t *>(arow + kbase + rq_perm64(off + 4)) = pk.y;
-            if ((w & 7) == 0) mrow[kbase >> 6] = prm.fmt == RQ_FMT_E4M3 ? __float_as_int(__fmul_rn((float) mi, 0.0625f)) : mi;
+            if ((w & 7) == 0) mrow[kbase >> 6] = multiplier_word<F8>(mi);
         }
-    }
+    };
+    if (prm.fmt == RQ_FMT_E4M3) store_codes(std::true_type{});
+    else store_codes(std::false_type{});
+    RQ_STAMP(tid == 0);                                     // 6: codes stored
+    RQ_STAMP_FLUSH(tid == 0, prm.status, 0x20);
 }
 
 template <typename Kern, typename... Args>
@@ -293,16 +283,21 @@ cudaError_t launch_ex(Kern kern, dim3 grid, dim3 block, size_t smem, int cluster
 
 constexpr size_t SMEM_LIMIT = 220 * 1024;
 
+template <typename Kern>
+cudaError_t configure_kernel(Kern kern) {
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
+}
+
 template <int P>
 cudaError_t configure() {
-    cudaError_t e = cudaFuncSetAttribute(rq_act_kernel<P, ACT_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
+    cudaError_t e = configure_kernel(rq_act_kernel<P, ACT_THREADS>);
     if (e != cudaSuccess) return e;
     if (P <= 20) {
-        e = cudaFuncSetAttribute(rq_act_kernel<(P <= 20 ? P : 1), 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
+        e = configure_kernel(rq_act_kernel<(P <= 20 ? P : 1), 1024>);
         if (e != cudaSuccess) return e;
     }
     if (P == 1) return e;
-    return cudaFuncSetAttribute(rq_act_cluster_kernel<(P > 1 ? P : 12)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) SMEM_LIMIT);
+    return configure_kernel(rq_act_cluster_kernel<(P > 1 ? P : 12), cluster_threads(P > 1 ? P : 12)>);
 }
 
 template <int P>
@@ -320,15 +315,14 @@ cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
     static const int min_p = getenv("RQ_TUNE_ACT_MINP") ? atoi(getenv("RQ_TUNE_ACT_MINP")) : 0;
     if (P > 1 && P >= min_p && prm.a8 != nullptr && prm.rot_out == nullptr && prm.G == 64 && prm.m % 64 == 0 && M <= 32) {
         // decode widths: a cluster per token
-        const int T = K / (64 * P), NB = P / 4, nchunks = K / prm.m;
+        constexpr int CP = P > 1 ? P : 12, CT = cluster_threads(CP);
+        const int units = (K / prm.n_rot) * (prm.m / 64) * (CP / 4);
         int C = 8;
-        while (C > 1 && !((C % T == 0 && C / T <= NB) || T % C == 0)) C >>= 1;
-        const int cps = C >= T ? C / T : 1, nsl = C >= T ? 1 : T / C;
-        const int slots = (nchunks + C - 1) / C, nb_max = (NB + cps - 1) / cps;
-        const size_t smem = ((size_t) slots * prm.m + (size_t) P * P + (size_t) P * 64 + (size_t) nsl * nb_max * 4 * 64) * sizeof(float);
+        while (C > 1 && units < 2 * C) C >>= 1;
+        const int units_max = (units + C - 1) / C;
+        const size_t smem = ((size_t) K + (size_t) CP * CP + (size_t) units_max * 4 * 64) * sizeof(float);
         if (C > 1 && smem <= SMEM_LIMIT) {
-            return launch_ex(rq_act_cluster_kernel<(P > 1 ? P : 12)>, dim3((unsigned) C, (unsigned) M), dim3(ACT_THREADS), smem, C,
-                             stream, prm, slots, cps, nsl, nb_max);
+            return launch_ex(rq_act_cluster_kernel<CP, CT>, dim3((unsigned) C, (unsigned) M), dim3(CT), smem, C, stream, prm, units_max);
         }
     }
     const size_t smem = ((size_t) K + (P > 1 ? (size_t) P * P : 0)) * sizeof(float);

@@ -204,10 +204,10 @@ __device__ __forceinline__ void group_range(const float4 a, const float4 b, int 
     hi = __fmul_rn(mx, clip);
 }
 
-// the 8 codes of a word and the group's multiplier.  fmt RQ_FMT_I8: int8 8*(q - z); RQ_FMT_E4M3: the e4m3 byte of
-// (q - z), exact, for the fp8 tensor-core path
-__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, int fmt,
-                                             int & mi) {
+// the 8 codes of a word and the group's multiplier.  F8 false: int8 8*(q - z) (RQ_FMT_I8); true: the e4m3 byte of
+// (q - z), exact (RQ_FMT_E4M3, the fp8 tensor-core path)
+template <bool F8>
+__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, int & mi) {
     const float mf = fminf(fmaxf(ceilf(__fdiv_rn(__fmul_rn(__fsub_rn(hi, lo), 255.0f), R)), 1.0f), 255.0f);
     mi = (int) mf;
     const float inv = __fdiv_rn(1.0f, __fmul_rn((float) mi, unit));
@@ -218,10 +218,28 @@ __device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, flo
     for (int j = 0; j < 8; ++j) {
         const float qf = fminf(fmaxf(__fadd_rn(rintf(__fmul_rn(v[j], inv)), zf), 0.0f), 15.0f);
         const int dz = (int) qf - (int) zf;                                  // q - z in [-15, 15]
-        const uint32_t byte = fmt == RQ_FMT_E4M3 ? rq_e4m3_of_int(dz) : (uint32_t) ((RQ_ACT_SCALE * dz) & 0xFF);
+        const uint32_t byte = F8 ? rq_e4m3_of_int(dz) : (uint32_t) ((RQ_ACT_SCALE * dz) & 0xFF);
         pk[j >> 2] |= byte << (8 * (j & 3));
     }
     return make_uint2(pk[0], pk[1]);
+}
+// what the multiplier word holds: m_g, or for the fp8 path the f32 bits of m_g / 16 (exact)
+template <bool F8>
+__device__ __forceinline__ int multiplier_word(int mi) {
+    return F8 ? __float_as_int(__fmul_rn((float) mi, 0.0625f)) : mi;
+}
+
+// maximum over the CTA of a per-thread value >= 0: warp shuffles, one shared-memory round, result in every thread of
+// warp 0 (other warps get an unspecified value).  red: one float per warp.  Contains one CTA barrier.
+__device__ __forceinline__ float cta_max_warp0(float v, float * red, int tid, int nt) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    if (tid < 32) {
+        v = tid < (nt >> 5) ? red[tid] : 0.0f;
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    }
+    return v;
 }
 
 }  // namespace rq_act_dev

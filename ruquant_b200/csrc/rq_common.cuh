@@ -61,6 +61,47 @@ static inline rq_ws_layout rq_ws(int64_t K, int64_t M) {
     return l;
 }
 
+// Timeline diagnostics, compiled in with -DRQ_TRACE only: when the 64-bit word at status[2..3] holds a device
+// pointer, every call appends (global timer in ns, tag << 32 | CTA) to the buffer behind it ([0] = event count).
+#if defined(RQ_TRACE) && defined(__CUDACC__)
+__device__ __forceinline__ void rq_trace(const int32_t * status, unsigned tag) {
+    if (status == nullptr) return;
+    unsigned long long * buf = *reinterpret_cast<unsigned long long * const *>(status + 2);
+    if (buf == nullptr) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned long long i = atomicAdd(buf, 1ull);
+    if (i < (1ull << 16)) { buf[2 + 2 * i] = t; buf[3 + 2 * i] = ((unsigned long long) tag << 32) | blockIdx.x; }
+}
+// cheaper form for phases inside one kernel: time stamps collected in registers and appended at the end
+struct rq_stamps {
+    unsigned long long t[12];
+    int n;
+    __device__ __forceinline__ rq_stamps() : n(0) {}
+    __device__ __forceinline__ void mark() {
+        unsigned long long v;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+        if (n < 12) t[n++] = v;
+    }
+    __device__ __forceinline__ void flush(const int32_t * status, unsigned tag) {
+        if (status == nullptr) return;
+        unsigned long long * buf = *reinterpret_cast<unsigned long long * const *>(status + 2);
+        if (buf == nullptr) return;
+        const unsigned long long i = atomicAdd(buf, (unsigned long long) n);
+        for (int k = 0; k < n; ++k)
+            if (i + k < (1ull << 16)) { buf[2 + 2 * (i + k)] = t[k]; buf[3 + 2 * (i + k)] = ((unsigned long long) (tag + k) << 32) | blockIdx.x; }
+    }
+};
+#define RQ_STAMP_DECL rq_stamps rq_st
+#define RQ_STAMP(cond) do { if (cond) rq_st.mark(); } while (0)
+#define RQ_STAMP_FLUSH(cond, status, tag) do { if (cond) rq_st.flush(status, tag); } while (0)
+#else
+#define rq_trace(status, tag) ((void) 0)
+#define RQ_STAMP_DECL
+#define RQ_STAMP(cond) ((void) 0)
+#define RQ_STAMP_FLUSH(cond, status, tag) ((void) 0)
+#endif
+
 // Launchers (one per .cu file).  All enqueue on `stream` and return a cudaError_t.
 cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,
                           float clip, int G, int fmt, int8_t * a8, int32_t * msh, float * u, float * rot_out, int64_t ldo,

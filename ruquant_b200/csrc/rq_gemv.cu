@@ -96,6 +96,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
     extern __shared__ __align__(128) uint8_t dyn[];
     __shared__ uint64_t full[STAGES], empty[STAGES];
     __shared__ int abort_word;
+    __shared__ int fmt_word;     // the activation format the quantizer recorded (-1 until a spare producer lane has read it)
     uint8_t * ring = dyn;
     int * part = reinterpret_cast<int *>(dyn + STAGES * ST_BYTES);      // [2][CONSUMERS][32][4 * NT]
     volatile int * abort_flag = &abort_word;
@@ -111,16 +112,24 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(&empty[s])), "r"(SUBS) : "memory");
         }
         abort_word = 0;
+        fmt_word = -1;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) rq_trace(prm.status, 0x10);
 
     if (warp == CONSUMERS) {
         // ---- producer: bulk copies of up to 8 KB, gated only by ring space
         if (lane == 0) {
             int issued = 0;       // stages of this CTA's stream, all tiles
             bool ok = true;
+            // This kernel multiplies int8 activations; one quantized for the fp8 tensor-core path is refused (status 2, no
+            // stores).  The word is read here, off the consumers' path: they look at it only when a tile is complete.
+            auto read_format = [&]() {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                *reinterpret_cast<volatile int *>(&fmt_word) = prm.status != nullptr ? prm.status[1] : RQ_FMT_I8;
+            };
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
                 const int wi = job_of_tile(prm, tile);
                 const uint8_t * src = reinterpret_cast<const uint8_t *>(prm.job[wi].w4t) + (size_t) (tile - prm.tile_start[wi]) * ng64 * 512;
@@ -134,8 +143,10 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                                  :: "r"(smem_u32(ring + (size_t) s * ST_BYTES)), "l"(src + (size_t) st * ST_BYTES), "r"(bytes), "r"(bar) : "memory");
                     ++issued;
+                    if (issued == STAGES) read_format();      // the ring is full: nothing to issue until the consumers run
                 }
             }
+            if (issued < STAGES) read_format();
             if (*abort_flag) {   // let every copy that was issued land before the CTA's shared memory goes away
                 for (int c = issued > STAGES ? issued - STAGES : 0; c < issued; ++c) {
                     const long long t0 = clock64();
@@ -149,8 +160,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 
     // ---- consumers.  Everything below reads what the preceding kernel (the quantizer) wrote.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // this kernel multiplies int8 activations; one quantized for the fp8 tensor-core path is refused (status 2, no stores)
-    const bool fmt_ok = prm.status == nullptr || prm.status[1] == RQ_FMT_I8;
+    if (threadIdx.x == 0) rq_trace(prm.status, 0x11);
 
     // B fragments: token gid (+8 for the second tile); the quantizer stores each run of 64 inputs so that the 16
     // bytes at offset tig*16 are inputs {0,16,32,48} + tig*4 .. +3: b0, b1 of both MMAs in one 128-bit load.
@@ -295,6 +305,9 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                 for (int w = 0; w < CONSUMERS; ++w) v += pt[(w * 32 + lane) * 4 * NT + t * 4 + i];
                 tot[t][i] = v;
             }
+        int fmt = *reinterpret_cast<volatile int *>(&fmt_word);
+        for (int spin = 0; fmt < 0 && spin < (1 << 20); ++spin) fmt = *reinterpret_cast<volatile int *>(&fmt_word);
+        const bool fmt_ok = fmt == RQ_FMT_I8;
         if (!fmt_ok && lane == 0) atomicExch(prm.status, 2);
         const float s_lo = row_lo < jb.N ? __ldg(jb.sw + row_lo) : 0.0f;
         const float s_hi = row_hi < jb.N ? __ldg(jb.sw + row_hi) : 0.0f;
@@ -311,6 +324,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
             }
         }
     }
+    if (threadIdx.x == 0) rq_trace(prm.status, 0x13);
 }
 
 template <int NT, int GS, bool HAS_K, bool ONE>
@@ -334,7 +348,10 @@ cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
     }
     cudaLaunchConfig_t cfg = {};
     const int tiles = prm.tile_start[prm.n_jobs];
-    const int resident = dev < 64 ? per_sm[dev] : 148;
+    // The quantizer ahead of this kernel (a cluster of up to 8 CTAs per token) still holds its shared memory when this
+    // grid starts: CTAs beyond the free slots would start only after it, with their whole share of tiles still to do.
+    static const int reserve = getenv("RQ_TUNE_GEMV_RESERVE") ? atoi(getenv("RQ_TUNE_GEMV_RESERVE")) : 8;
+    const int resident = (dev < 64 ? per_sm[dev] : 148) - reserve;
     cfg.gridDim = dim3((unsigned) (tiles < resident ? tiles : resident));
     cfg.blockDim = dim3((CONSUMERS + 1) * 32);
     cfg.dynamicSmemBytes = smem;
