@@ -38,7 +38,9 @@ def build(force=False, verbose=False):
         path = os.path.join(CSRC, src)
         if not os.path.exists(path):
             continue
-        obj = os.path.join(CSRC, src[:-3] + (".o" if not os.environ.get("RQ_B200_LIB") else "." + os.path.basename(LIB) + ".o"))
+        # a side-by-side build keeps its objects next to its own output file
+        obj = (os.path.join(CSRC, src[:-3] + ".o") if not os.environ.get("RQ_B200_LIB")
+               else os.path.join(os.path.dirname(os.path.abspath(LIB)), src[:-3] + "." + os.path.basename(LIB) + ".o"))
         cmd = ([nvcc] + NVCC_FLAGS + os.environ.get("RQ_NVCC_EXTRA", "").split() + (["-Xptxas", "-v"] if verbose else [])
                + ["-c", path, "-o", obj])
         procs.append((cmd, subprocess.Popen(cmd)))

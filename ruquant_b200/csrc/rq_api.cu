@@ -164,7 +164,7 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_prepare(const void
                               (layouts & RQ_PREPACK_PREFILL) ? reinterpret_cast<int8_t *>(pp + l.off_w8) : nullptr,
                               reinterpret_cast<int8_t *>(pp + l.off_wk), out->wk_mode, stream));
     if (layouts & RQ_PREPACK_PREFILL) {
-        if (rq_encode_tmap_i8(out->tmap_w8, pp + l.off_w8, K, N, 256) != 0) return RQ_ERR_CUDA;
+        if (rq_encode_tmap_i8(out->tmap_w8, pp + l.off_w8, K, N, 128)   /* box: half a tile of weight rows */ != 0) return RQ_ERR_CUDA;
     }
     RQ_CUDA(cudaStreamSynchronize(stream));
     return RQ_OK;

@@ -92,11 +92,27 @@ struct rq_stamps {
             if (i + k < (1ull << 16)) { buf[2 + 2 * (i + k)] = t[k]; buf[3 + 2 * (i + k)] = ((unsigned long long) (tag + k) << 32) | blockIdx.x; }
     }
 };
+// cycle counters around waits: RQ_CYC_REPORT appends (cycles, tag << 32 | CTA)
+#define RQ_CYC_DECL(name) long long name = 0, name##_t0 = 0
+#define RQ_CYC_BEGIN(name) name##_t0 = clock64()
+#define RQ_CYC_END(name) name += clock64() - name##_t0
+#define RQ_CYC_REPORT(status, tag, name) rq_trace_value(status, tag, (unsigned long long) (name))
+__device__ __forceinline__ void rq_trace_value(const int32_t * status, unsigned tag, unsigned long long value) {
+    if (status == nullptr) return;
+    unsigned long long * buf = *reinterpret_cast<unsigned long long * const *>(status + 2);
+    if (buf == nullptr) return;
+    const unsigned long long i = atomicAdd(buf, 1ull);
+    if (i < (1ull << 16)) { buf[2 + 2 * i] = value; buf[3 + 2 * i] = ((unsigned long long) tag << 32) | (blockIdx.x + gridDim.x * blockIdx.y); }
+}
 #define RQ_STAMP_DECL rq_stamps rq_st
 #define RQ_STAMP(cond) do { if (cond) rq_st.mark(); } while (0)
 #define RQ_STAMP_FLUSH(cond, status, tag) do { if (cond) rq_st.flush(status, tag); } while (0)
 #else
 #define rq_trace(status, tag) ((void) 0)
+#define RQ_CYC_DECL(name)
+#define RQ_CYC_BEGIN(name) ((void) 0)
+#define RQ_CYC_END(name) ((void) 0)
+#define RQ_CYC_REPORT(status, tag, name) ((void) 0)
 #define RQ_STAMP_DECL
 #define RQ_STAMP(cond) ((void) 0)
 #define RQ_STAMP_FLUSH(cond, status, tag) ((void) 0)
