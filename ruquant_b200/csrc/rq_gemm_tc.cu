@@ -115,24 +115,26 @@ constexpr uint32_t IDESC_F8_PAIR = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((
 template <bool F8, bool PAIR, bool ACC>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db) {
     constexpr uint32_t idesc = PAIR ? (F8 ? IDESC_F8_PAIR : IDESC_PAIR) : (F8 ? IDESC_F8 : IDESC);
+    // called by the whole (converged) warp with warp-uniform operands; one elected lane issues
     if (PAIR) {
-        if (F8) asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        if (F8) asm volatile("{\n\t.reg .pred pe, p;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@pe tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
                              :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
-        else    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        else    asm volatile("{\n\t.reg .pred pe, p;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@pe tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                              :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
     } else {
-        if (F8) asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        if (F8) asm volatile("{\n\t.reg .pred pe, p;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@pe tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
                              :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
-        else    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        else    asm volatile("{\n\t.reg .pred pe, p;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t@pe tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                              :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "n"(ACC ? 1 : 0) : "memory");
     }
 }
+// the commits, like the MMAs, are called by the whole warp and issued by one elected lane
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+    asm volatile("{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" :: "r"(bar) : "memory");
 }
 // the pair's commit arrives on the barrier at this offset in both CTAs (a commit, not a copy: nothing is loaded)
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+    asm volatile("{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}"
                  :: "r"(bar), "h"((uint16_t) 3) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -317,8 +319,9 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && leader) {
-            // Straight-line issue loop: shifts instead of divisions (gsteps is 1, 2 or 4), slot, phase and accumulator
+        if (leader) {
+            // The whole warp walks the loop with warp-uniform values (descriptors and addresses then live in the uniform
+            // datapath) and elects a lane at each MMA and commit.  Straight-line issue loop: shifts instead of divisions (gsteps is 1, 2 or 4), slot, phase and accumulator
             // buffer as running counters, descriptors advanced by adding to their address field.
             const uint32_t gmask = (uint32_t) gsteps - 1u;
             const uint64_t da0 = umma_desc(ring), db0 = umma_desc(ring + A_BYTES);
@@ -333,7 +336,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int v = first; v < units && ok; v += stride) {
                 for (int ks = 0; ks < n_ks && ok; ++ks) {
                     RQ_CYC_BEGIN(c_full);
-                    if (!mbar_wait(smem_u32(&sh.full[s]), ph, abort_flag)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.full[s]), ph, abort_flag))) { ok = false; break; }
                     RQ_CYC_END(c_full);
                     tc_fence_after();
                     const uint64_t so = (uint64_t) ((s * STAGE_BYTES) >> 4);
@@ -345,7 +348,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         const uint32_t d = tmem_base + buf * BN;
                         if (gs == 0) {
                             RQ_CYC_BEGIN(c_tmem);
-                            if (!mbar_wait(smem_u32(&sh.tmem_empty[buf]), ((gcount >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_empty[buf]), ((gcount >> 1) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
                             RQ_CYC_END(c_tmem);
                             tc_fence_after();
                             RQ_CYC_BEGIN(c_issue);
@@ -372,11 +375,13 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
             }
             RQ_CYC_END(c_mma);
+            if (lane == 0) {
             RQ_CYC_REPORT(prm.status, 0x42, c_full);
             RQ_CYC_REPORT(prm.status, 0x43, c_tmem);
             RQ_CYC_REPORT(prm.status, 0x44, c_mma);
             RQ_CYC_REPORT(prm.status, 0x47, c_issue);
             RQ_CYC_REPORT(prm.status, 0x48, c_commit);
+            }
         }
     }
     } else {
