@@ -158,6 +158,17 @@ int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off
  * up on a bounded wait.  Not capture-safe. */
 int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream);
 
+/* The reference's weight quantizer on the GPU: N rows of K fp32 (rows ldw floats apart) -> N rows of K/256 blocks,
+ * byte for byte what quantize_w4a4 / quantize_w4a4h write (patch:2775-2789; per row quantize_row_w4a4_ref /
+ * quantize_row_w4a4h_ref, patch:2681-2710; scale search and packing rq_scale_search, rq_quantize_row_w, rq_pack,
+ * patch:2489-2580).  wgroup: 0 = one scale per row, 256 / 64 = the reference's RQ_WGROUP=1 / 64 (a multiplier per block
+ * / per 64 inputs).  rot_blocks: RQ_ROT_BLOCKS (W4A4H rows are rotated in blocks of K / rot_blocks when that divides
+ * K).  The activation clip in the headers is left unset (0), as the reference leaves it.  scratch: caller-owned,
+ * 256-byte aligned, rq_w4a4_quantize_weights_scratch_bytes (0 on a bad request).  Enqueues on stream. */
+size_t rq_w4a4_quantize_weights_scratch_bytes(int type, int64_t K, int64_t N, int wgroup);
+int rq_w4a4_quantize_weights(const float * w_dev, int64_t ldw, int type, int64_t K, int64_t N, int wgroup, int rot_blocks,
+                             void * blocks_dev, void * scratch_dev, size_t scratch_bytes, void * stream);
+
 /* No counterpart in the reference.  The MUL_MAT node for callers that may not allocate device memory (a backend
  * whose buffers are planned ahead of time, a plug-in inside another runtime's stream): the scratch that
  * rq_w4a4_mul_mat takes from the caller lives in a fixed array inside the library instead.  One weight, M <= 16

@@ -22,6 +22,7 @@ EXPORTS = [
     "rq_w4a4_prepare", "rq_w4a4_workspace_bytes", "rq_w4a4_mul_mat", "rq_w4a4_mul_mat_quantized", "rq_w4a4_rotate",
     "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
     "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n", "rq_w4a4_act_format",
+    "rq_w4a4_quantize_weights", "rq_w4a4_quantize_weights_scratch_bytes",
 ]
 
 
@@ -74,6 +75,9 @@ def lib():
         L.rq_w4a4_rotate.argtypes = [vp, i64, i64, i64, i64, vp, i64, vp]
         L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, i32, vp, sz, vp]
         L.rq_w4a4_act_format.argtypes = [ctypes.POINTER(pd), i32, i64, i32]
+        L.rq_w4a4_quantize_weights_scratch_bytes.argtypes = [i32, i64, i64, i32]
+        L.rq_w4a4_quantize_weights_scratch_bytes.restype = sz
+        L.rq_w4a4_quantize_weights.argtypes = [vp, i64, i32, i64, i64, i32, i32, vp, vp, sz, vp]
         u64p = ctypes.POINTER(ctypes.c_uint64)
         L.rq_w4a4_workspace_layout.argtypes = [i64, i64, i32, u64p, u64p, u64p, u64p]
         L.rq_w4a4_device_status.argtypes = [vp, i64, i64, vp]
@@ -226,6 +230,23 @@ def act_format(weights, M, path=PATH_AUTO):
     fmt = lib().rq_w4a4_act_format(descs, len(ws_list), M, path)
     _check(min(fmt, 0), "rq_w4a4_act_format")
     return fmt
+
+
+def quantize_weights(w, type_, wgroup=0, rot_blocks=1, stream=None):
+    """Rows of fp32 weights (CUDA, [N, K]) -> the reference's blocks as a uint8 tensor [N, K/256*144]."""
+    import torch
+    if not w.is_cuda or w.dtype != torch.float32 or w.dim() != 2 or w.stride(1) != 1:
+        raise ValueError("w must be a 2-D float32 CUDA tensor with unit inner stride")
+    N, K = w.shape
+    nbytes = lib().rq_w4a4_quantize_weights_scratch_bytes(type_, K, N, wgroup)
+    if nbytes == 0:
+        raise RqError(-2, "rq_w4a4_quantize_weights_scratch_bytes")
+    with torch.cuda.device(w.device):
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+        out = torch.empty((N, K // BLOCK_CODES * BLOCK_BYTES), dtype=torch.uint8, device=w.device)
+        _check(lib().rq_w4a4_quantize_weights(w.data_ptr(), w.stride(0), type_, K, N, wgroup, rot_blocks, out.data_ptr(),
+                                              scratch.data_ptr(), nbytes, _stream_ptr(stream)), "rq_w4a4_quantize_weights")
+    return out
 
 
 def quantize(x, n_rot, clip, group=64, workspace=None, stream=None, fmt=FMT_I8):

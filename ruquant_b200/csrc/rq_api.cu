@@ -208,6 +208,54 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_rotate(const float
     return RQ_OK;
 }
 
+// scratch of the weight quantizer: [rotated rows, W4A4H only][one scale per row or per weight group]
+static void rq_wq_scratch(int type, int64_t K, int64_t N, int wgroup, uint64_t * off_sg, uint64_t * bytes) {
+    const uint64_t rot = type == RQ_TYPE_W4A4H ? rq_align256((uint64_t) N * K * 4) : 0;
+    const uint64_t ng = wgroup ? (uint64_t) (K / wgroup) : 1;
+    *off_sg = rot;
+    *bytes = rot + rq_align256((uint64_t) N * ng * 4);
+}
+
+extern "C" __attribute__((visibility("default"))) size_t rq_w4a4_quantize_weights_scratch_bytes(int type, int64_t K, int64_t N, int wgroup) {
+    if ((type != RQ_TYPE_W4A4 && type != RQ_TYPE_W4A4H) || K <= 0 || K % RQ_BLOCK_CODES != 0 || K > RQ_MAX_K || N < 1 ||
+        (wgroup != 0 && wgroup != 64 && wgroup != 256)) return 0;
+    uint64_t off = 0, bytes = 0;
+    rq_wq_scratch(type, K, N, wgroup, &off, &bytes);
+    return (size_t) bytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize_weights(const float * w_dev, int64_t ldw, int type, int64_t K, int64_t N, int wgroup,
+                                        int rot_blocks, void * blocks_dev, void * scratch_dev, size_t scratch_bytes,
+                                        void * stream) {
+    if (type != RQ_TYPE_W4A4 && type != RQ_TYPE_W4A4H) return RQ_ERR_ARG;
+    int rc = rq_check_x(w_dev, ldw, N, K);
+    if (rc != RQ_OK) return rc;
+    if (wgroup != 0 && wgroup != 64 && wgroup != 256) return RQ_ERR_GROUP;
+    if (blocks_dev == nullptr || scratch_dev == nullptr || (reinterpret_cast<uintptr_t>(scratch_dev) & 255) != 0) return RQ_ERR_ARG;
+    uint64_t off_sg = 0, need = 0;
+    rq_wq_scratch(type, K, N, wgroup, &off_sg, &need);
+    if (scratch_bytes < need) return RQ_ERR_WORKSPACE;
+    uint8_t * sc = static_cast<uint8_t *>(scratch_dev);
+    const float * rows = w_dev;
+    int64_t ld = ldw;
+    int pad0 = (int) K;
+    if (type == RQ_TYPE_W4A4H) {
+        // block-diagonal rotation of K / rot_blocks wide blocks when that divides K (rq_rot_len, patch:2687-2694)
+        const int64_t n_rot = (rot_blocks > 1 && K % rot_blocks == 0) ? K / rot_blocks : K;
+        int p = 0, m = 0;
+        if (!rq_hadamard_factor(n_rot, &p, &m)) return RQ_ERR_ROTATION;
+        float * rot = reinterpret_cast<float *>(sc);
+        RQ_CUDA(rq_launch_act(w_dev, ldw, N, K, (int) n_rot, p, m, 1.0f / sqrtf((float) n_rot), 1.0f, 64, RQ_FMT_I8, nullptr, nullptr,
+                              nullptr, rot, K, nullptr, (cudaStream_t) stream));
+        rows = rot;
+        ld = K;
+        pad0 = (int) n_rot;
+    }
+    RQ_CUDA(rq_launch_wquant(rows, ld, N, K, wgroup, pad0, reinterpret_cast<float *>(sc + off_sg),
+                             static_cast<rq_block *>(blocks_dev), (cudaStream_t) stream));
+    return RQ_OK;
+}
+
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float clip,
                                 int act_group, int act_format, void * workspace_dev, size_t workspace_bytes, void * stream) {
     if (act_format != RQ_FMT_I8 && act_format != RQ_FMT_E4M3) return RQ_ERR_ARG;

@@ -139,6 +139,9 @@ cudaError_t rq_launch_gemv(const rq_gemv_job * jobs, int n_jobs, int64_t K, cons
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
+// weight quantizer: scale search + pack of already-rotated rows (rq_wquant.cu)
+cudaError_t rq_launch_wquant(const float * x, int64_t ldx, int64_t n_rows, int64_t K, int wgroup, int pad0, float * sg,
+                             rq_block * out, cudaStream_t stream);
 // per-device kernel attributes (large dynamic shared memory); called from rq_w4a4_prepare so that the first
 // launch inside a stream capture has nothing left to set up
 cudaError_t rq_configure_act();
