@@ -356,6 +356,53 @@ def run_ours(args):
         os._exit(0)
 
 
+def run_wquant(args):
+    """The GPU weight quantizer on N rows of K against the reference's CPU quantizer on a sample of the same rows."""
+    import torch
+
+    import oracle
+    import ruquant_b200 as rq
+
+    parts = [int(v) for v in args.wquant.split(",")]
+    K, N = parts[:2]
+    type_ = parts[2] if len(parts) > 2 else rq.TYPE_W4A4H
+    wgroup = parts[3] if len(parts) > 3 else 0
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4242)
+    w = torch.randn((N, K), generator=g, device="cuda", dtype=torch.float32) * 0.02
+    for _ in range(2):
+        blocks = rq.quantize_weights(w, type_, wgroup)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(3, args.steps // 4)
+    e0.record()
+    for _ in range(reps):
+        blocks = rq.quantize_weights(w, type_, wgroup)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    # CPU: the reference's own code where it was compiled here (no weight-group modes there), else the port
+    sample = min(N, 256)
+    ws = w[:sample].cpu().numpy()
+    if oracle.have_ref() and wgroup == 0:
+        cpu, kind = oracle.Ref(), "reference"
+        fn = lambda: cpu.quantize_weights(ws, type_)
+    else:
+        cpu, kind = oracle.Port(), "port"
+        fn = lambda: cpu.quantize_weights(ws, type_, wgroup=wgroup)
+    best = float("inf")
+    for _ in range(3):
+        t0 = time.perf_counter()
+        want = fn()
+        best = min(best, time.perf_counter() - t0)
+    same = bool((blocks[:sample].cpu().numpy() == want).all())
+    print(json.dumps({"wquant": {"K": K, "N": N, "type": type_, "wgroup": wgroup}, "ms": ms, "rows_per_s": N / (ms * 1e-3),
+                      "GBps_fp32_in": N * K * 4 / (ms * 1e-3) / 1e9,
+                      "cpu": {"rows_per_s": sample / best, "cores": os.cpu_count(), "kind": kind, "sample_rows": sample},
+                      "bit_identical_on_sample": same}))
+
+
 def run_single(args):
     """One shape, K,N,M[,type]: a CUDA graph of back-to-back matmuls over enough distinct weight copies to overflow
     L2 (the method of the reference's own bench, rig/ggml_bench.cpp), whole node and contraction kernel alone."""
@@ -437,11 +484,14 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--single", default="", help="K,N,M[,type]: time one shape instead of the stack")
+    ap.add_argument("--wquant", default="", help="K,N[,type[,wgroup]]: time the GPU weight quantizer beside the reference's CPU code")
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--group", type=int, default=64)
     ap.add_argument("--path", type=int, default=0)
     args = ap.parse_args()
-    if args.single:
+    if args.wquant:
+        run_wquant(args)
+    elif args.single:
         run_single(args)
     elif args.impl == "reference":
         run_reference(args)
