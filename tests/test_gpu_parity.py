@@ -331,3 +331,35 @@ def test_status_codes(rq, port):
     with pytest.raises(rq.RqError) as e:      # weight groups of 64 need activation groups of 64
         rq.mul_mat(w64, torch.zeros((1, 512), dtype=torch.float32, device="cuda"), act_group=128)
     assert e.value.status == -4
+
+
+# ------------------------------------------------------------------------------------------- column (K) split
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_column_split_partials_sum_in_rank_order(rq, port, world):
+    """The reference's tensor-parallel mode for attn_output / ffn_down: every rank multiplies its block columns by its
+    slice of x (quantized on its own) and the partials are summed in rank order.  One GPU plays all ranks in turn."""
+    from ruquant_b200 import shard
+    K, N, M = 5120 * 2, 96, 5
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9300), 45, rot_blocks=world)    # rotation length K / world
+    x = inputs.outlier_activations(M, K, 9301)
+    ks = K // world
+    got, want = None, None
+    for r in range(world):
+        cols = np.ascontiguousarray(shard.col_shard(wb, N, K, r, world))
+        xs = np.ascontiguousarray(x[:, r * ks:(r + 1) * ks])
+        p_gpu = torch.from_numpy(gpu_mul_mat(rq, cols, 45, ks, xs))
+        p_cpu = port.mul_mat(cols, 45, ks, xs)
+        got = p_gpu if got is None else got + p_gpu
+        want = p_cpu if want is None else want + p_cpu
+    assert_bits(got.numpy(), want, "column split over %d" % world)
+
+
+def test_column_split_needs_rotation_blocks(rq, port):
+    from ruquant_b200 import shard
+    K, N = 2048, 32
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9310), 45)         # rotated over the whole row
+    cols = np.ascontiguousarray(shard.col_shard(wb, N, K, 0, 2))
+    with pytest.raises(rq.RqError) as e:
+        rq.Weight(dev(cols).view(-1), 45, K // 2, N=N)
+    assert e.value.status == -3
