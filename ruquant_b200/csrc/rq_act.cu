@@ -32,8 +32,9 @@ namespace cg = cooperative_groups;
 namespace {
 
 constexpr int ACT_THREADS = 256;
-// threads of a cluster CTA: a thread of the Paley stage keeps P inputs in registers
-constexpr int cluster_threads(int p) { return p <= 72 ? 512 : 256; }
+// threads of a cluster CTA: every phase is latency, so as many warps as the Paley stage's registers allow (it reads its
+// P inputs once each, the compiler keeps them at about 55-64 registers)
+constexpr int cluster_threads(int p) { return p <= 72 ? 1024 : 512; }
 
 using namespace rq_act_dev;
 
@@ -317,7 +318,8 @@ cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
         // decode widths: a cluster per token
         constexpr int CP = P > 1 ? P : 12, CT = cluster_threads(CP);
         const int units = (K / prm.n_rot) * (prm.m / 64) * (CP / 4);
-        int C = 8;
+        static const int c_max = getenv("RQ_TUNE_ACT_CMAX") ? atoi(getenv("RQ_TUNE_ACT_CMAX")) : 8;
+        int C = c_max;
         while (C > 1 && units < 2 * C) C >>= 1;
         const int units_max = (units + C - 1) / C;
         const size_t smem = ((size_t) K + (size_t) CP * CP + (size_t) units_max * 4 * 64) * sizeof(float);
