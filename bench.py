@@ -315,36 +315,41 @@ def run_ours(args):
     e2e = {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": ms_e2e, "copy_overlap": "%d layer chunks, copies on two streams beside the compute" % n_chunks}
 
-    # ---- prefill: M = 4096 gate/up-shaped GEMM, whole node and GEMM kernel alone
+    # ---- prefill: the M = 4096 gate/up-shaped and down-shaped GEMMs, whole node and GEMM kernel alone
     prefill = None
     if not args.no_prefill:
+        def prefill_leg(K, N, M, seed):
+            nl = N // world
+            blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=seed + rank, device=dev)
+            w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_PREFILL)
+            del blocks
+            g = torch.Generator(device=dev)
+            g.manual_seed(99)
+            x = torch.randn((M, K), generator=g, device=dev, dtype=torch.float32)
+            y = torch.empty((M, nl), device=dev, dtype=torch.float32)
+            y_all = torch.empty((world, M, nl), device=dev, dtype=torch.float32) if world > 1 else None
+            ws = rq.new_workspace(K, M, dev)
+
+            def node():
+                rq.mul_mat(w, x, out=y, clip=1.0, act_group=64, workspace=ws, stream=stream)
+                if world > 1:
+                    dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
+
+            def gemm_only():
+                rq.mul_mat_quantized(w, M, ws, out=y, act_group=64, stream=stream)
+
+            ms_node = timed(node, max(3, args.steps), 3)
+            ms_gemm = timed(gemm_only, max(3, args.steps), 3)
+            rq.device_status(ws, K, M)
+            ops = 2.0 * M * N * K
+            return {"workload": "W4A4H K=%d N=%d M=%d" % (K, N, M), "tops_node": ops / (ms_node * 1e-3) / 1e12, "ms_node": ms_node,
+                    "tops_gemm_kernel": 2.0 * M * nl * K / (ms_gemm * 1e-3) / 1e12 * world, "ms_gemm_kernel": ms_gemm,
+                    "int8_dense_peak_nominal_tops": 4500.0 * world,
+                    "frac_of_nominal_int8_peak": ops / (ms_node * 1e-3) / 1e12 / (4500.0 * world)}
+
         _, K, N, M = PREFILL
-        nl = N // world
-        blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=424242 + rank, device=dev)
-        w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_PREFILL)
-        g = torch.Generator(device=dev)
-        g.manual_seed(99)
-        x = torch.randn((M, K), generator=g, device=dev, dtype=torch.float32)
-        y = torch.empty((M, nl), device=dev, dtype=torch.float32)
-        y_all = torch.empty((world, M, nl), device=dev, dtype=torch.float32) if world > 1 else None
-        ws = rq.new_workspace(K, M, dev)
-
-        def node():
-            rq.mul_mat(w, x, out=y, clip=1.0, act_group=64, workspace=ws, stream=stream)
-            if world > 1:
-                dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
-
-        def gemm_only():
-            rq.mul_mat_quantized(w, M, ws, out=y, act_group=64, stream=stream)
-
-        ms_node = timed(node, max(3, args.steps), 3)
-        ms_gemm = timed(gemm_only, max(3, args.steps), 3)
-        rq.device_status(ws, K, M)
-        ops = 2.0 * M * N * K
-        prefill = {"workload": "W4A4H K=5120 N=17408 M=4096", "tops_node": ops / (ms_node * 1e-3) / 1e12, "ms_node": ms_node,
-                   "tops_gemm_kernel": 2.0 * M * nl * K / (ms_gemm * 1e-3) / 1e12 * world, "ms_gemm_kernel": ms_gemm,
-                   "int8_dense_peak_nominal_tops": 4500.0 * world,
-                   "frac_of_nominal_int8_peak": ops / (ms_node * 1e-3) / 1e12 / (4500.0 * world)}
+        prefill = prefill_leg(K, N, M, 424242)
+        prefill["down_shaped"] = prefill_leg(N, K, M, 434343)      # K = 17408 (68 x 256 rotation), N = 5120
 
     # ---- CPU baseline beside it (rank 0, one GPU): one layer on the host cores
     cpu = None

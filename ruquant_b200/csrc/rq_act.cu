@@ -88,6 +88,19 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
         const int m = prm.m;
         if constexpr (P > 1) {
             const int ncol = K / P, n = prm.n_rot;
+            if constexpr (P <= 20 && THREADS <= 256) {
+                // many tokens in flight (one CTA each): the adds themselves are the work, signs folded into the code
+                for (int c = tid; c < ncol; c += nt) {
+                    const int blk = c / m, j = c - blk * m;
+                    float * b = buf + (size_t) blk * n + j;
+                    float acc[P];
+#pragma unroll
+                    for (int a = 0; a < P; ++a) acc[a] = 0.0f;
+                    paley_static<P>(b, m, acc, std::make_index_sequence<P>{});
+#pragma unroll
+                    for (int a = 0; a < P; ++a) b[a * m] = __fmul_rn(acc[a], prm.rot_scale);
+                }
+            } else
             for (int c = tid; c < ncol; c += nt) {
                 const int blk = c / m, j = c - blk * m;
                 float * b = buf + (size_t) blk * n + j;
@@ -96,7 +109,8 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
                 for (int i = 0; i < P; ++i) col[i] = b[i * m];
                 for (int a0 = 0; a0 < P; a0 += 4) {
                     float out[4];
-                    paley_block4<P>(col, table, a0, prm.rot_scale, out);
+                    if (THREADS <= 256 && a0 > 0) paley_block4_const<P>(col, a0, prm.rot_scale, out);   // block 0 holds the irregular output 0
+                    else paley_block4<P>(col, table, a0, prm.rot_scale, out);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) b[(a0 + k) * m] = out[k];
                 }

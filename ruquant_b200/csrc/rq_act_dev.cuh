@@ -3,6 +3,8 @@
 // Bit-parity contract: see rq_act.cu.
 #pragma once
 
+#include <utility>
+
 #include "rq_common.cuh"
 
 namespace rq_act_dev {
@@ -29,6 +31,66 @@ __device__ __forceinline__ void build_sign_table(float * table, signed char * ch
         else plus = chi[(((a - i) % q) + q) % q] > 0;
         table[e] = plus ? 1.0f : -1.0f;
     }
+}
+
+// ---- the same signs at compile time.  chi(r) = +1 when r is a non-zero square mod q = P - 1.
+template <int P>
+__host__ __device__ constexpr bool paley_plus(int i, int a) {
+    if (i == a || i == 0) return true;
+    if (a == 0) return false;
+    const int q = P - 1;
+    const int r = (((a - i) % q) + q) % q;
+    for (int t = 1; t < q; ++t) if ((t * t) % q == r) return true;
+    return false;
+}
+// All P outputs of one column, fully unrolled: acc[a] += x_i or acc[a] -= x_i with the choice made by the compiler, so
+// a term is one add and nothing else (the table-driven form spends a shared-memory wavefront per 32-bit sign, which is
+// what bounds it when thousands of tokens are rotated).  Ascending i per output, from 0.0f, as the reference sums.
+template <int P, int I, size_t... A>
+__device__ __forceinline__ void paley_static_row(float x, float (&acc)[P], std::index_sequence<A...>) {
+    ((acc[A] = paley_plus<P>(I, (int) A) ? __fadd_rn(acc[A], x) : __fsub_rn(acc[A], x)), ...);
+}
+template <int P, size_t... I>
+__device__ __forceinline__ void paley_static(const float * b, int m, float (&acc)[P], std::index_sequence<I...>) {
+    (paley_static_row<P, (int) I>(b[I * m], acc, std::make_index_sequence<P>{}), ...);
+}
+
+// The Paley matrix is circulant away from its first row and column: for i, a >= 1 the sign of input chunk i in output
+// chunk a depends only on a - i.  ext[d + q - 1], d = a - i in (-q, q), holds it (+1 at d = 0, the identity's share), a
+// table of 2q - 1 floats that lives in constant memory: a warp walks the output blocks together, so the index is
+// warp-uniform and the sign comes through the constant cache instead of costing a shared-memory wavefront per term.
+template <int P>
+struct PaleyExt {
+    float v[2 * (P - 1) - 1];
+    constexpr PaleyExt() : v() {
+        const int q = P - 1;
+        for (int d = -(q - 1); d <= q - 1; ++d) {
+            const int r = ((d % q) + q) % q;
+            bool plus = d == 0;
+            for (int t = 1; t < q && !plus; ++t) plus = (t * t) % q == r;
+            v[d + q - 1] = plus ? 1.0f : -1.0f;
+        }
+    }
+};
+template <int P> __constant__ PaleyExt<P> c_paley_ext = PaleyExt<P>();
+
+// outputs a0 .. a0+3 (a0 >= 1, warp-uniform) of one column held in registers, signs from the constant table
+template <int P>
+__device__ __forceinline__ void paley_block4_const(const float (&col)[P], int a0, float scale, float (&out)[4]) {
+    // i = 0 enters every output with +
+    float acc0 = __fadd_rn(0.0f, col[0]), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+    const float * e = c_paley_ext<P>.v + (a0 + P - 2);          // e[k - i] = sign of input i in output a0 + k
+#pragma unroll
+    for (int i = 1; i < P; ++i) {
+        acc0 = __fmaf_rn(col[i], e[0 - i], acc0);
+        acc1 = __fmaf_rn(col[i], e[1 - i], acc1);
+        acc2 = __fmaf_rn(col[i], e[2 - i], acc2);
+        acc3 = __fmaf_rn(col[i], e[3 - i], acc3);
+    }
+    out[0] = __fmul_rn(acc0, scale);
+    out[1] = __fmul_rn(acc1, scale);
+    out[2] = __fmul_rn(acc2, scale);
+    out[3] = __fmul_rn(acc3, scale);
 }
 
 // outputs a0 .. a0+3 of one column held in registers: four independent chains, terms in ascending i

@@ -187,8 +187,10 @@ __device__ __forceinline__ void fold32_f8(float (&tf)[128], const int (&v)[32], 
 #pragma unroll
     for (int i = 0; i < 32; ++i) tf[BASE + i] = fma_rm(__int_as_float(v[i]), mf, tf[BASE + i]);
 }
-// Every 1024 inputs the float is re-centred: what it holds above +-2^19 moves, in units of 2^20, into a signed byte
-// of a packed carry word (at most 32 re-centrings of at most +-3 each), so the float never leaves its window.
+// Every 1536 inputs the float is re-centred: what it holds above +-2^19 moves, in units of 2^20, into a signed byte
+// of a packed carry word, so the float never leaves its window.  Bounds: a group of G inputs adds at most
+// 255 * (G*15*8) / 16 in magnitude, 2.94 M per 1536 inputs, on top of at most 2^19 left by the last re-centring:
+// |t - magic| < 3.5 M < 2^22; a re-centring moves at most 4 units, K <= 32768 has at most 22 of them: |byte| <= 88.
 __device__ __forceinline__ void recenter(float (&tf)[128], int (&carry)[32]) {
 #pragma unroll
     for (int i = 0; i < 128; ++i) {
@@ -391,7 +393,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // the quantizer records the format it wrote: refuse to multiply the wrong one
         const bool fmt_ok = prm.status == nullptr || prm.status[1] == (F8 ? RQ_FMT_E4M3 : RQ_FMT_I8);
         const uint32_t empty_bar0 = PAIR ? map_to_cta(smem_u32(&sh.tmem_empty[0]), 0) : smem_u32(&sh.tmem_empty[0]);
-        const int recenter_every = prm.G >= 1024 ? 1 : 1024 / prm.G;
+        const int recenter_every = 1536 / prm.G;           // G is 64, 128 or 256
         const bool vec = ((prm.ldy & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.y) & 15) == 0);
         uint32_t gcount = 0;              // accumulator groups folded (all units)
         bool ok = true;
@@ -436,7 +438,15 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     tmem_ld_wait(va); tmem_ld32(t0 + 32, vb); fold32_f8<0>(tf, va, mf);
                     tmem_ld_wait(vb); tmem_ld32(t0 + 64, va); fold32_f8<32>(tf, vb, mf);
                     tmem_ld_wait(va); tmem_ld32(t0 + 96, vb); fold32_f8<64>(tf, va, mf);
-                    tmem_ld_wait(vb);                         fold32_f8<96>(tf, vb, mf);
+                    tmem_ld_wait(vb);
+                    // the accumulator is in registers: hand the buffer back before the last piece is folded
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
+                        else      mbar_arrive(empty_bar0 + buf * 8u);
+                    }
+                    fold32_f8<96>(tf, vb, mf);
                 } else {
                     // software pipeline over the four 32-column chunks: the load of chunk c+1 is in flight while chunk c folds
                     int va[32], vb[32];
@@ -453,11 +463,13 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     tmem_ld_wait(vb);
                     fold32(tot, 96, vb, mm);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
-                    else      mbar_arrive(empty_bar0 + buf * 8u);
+                if constexpr (!F8) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
+                        else      mbar_arrive(empty_bar0 + buf * 8u);
+                    }
                 }
                 if constexpr (F8) {
                     if (++since == recenter_every || ag == n_ag - 1) { recenter(tf, carry); since = 0; }
