@@ -174,13 +174,40 @@ def run_ours(args):
     # pinned-host -> device copy and one device -> host copy around the captured graph
     k_layer = sum(LAYER_DIMS[names[0]][0] for names in GROUPS)
     x_arena = torch.empty((L * k_layer,), device=dev, dtype=torch.float32)
-    y_arena = torch.empty((L * world * n_layer_local,), device=dev, dtype=torch.float32)
+    # N > 1: every rank's output arena is mapped into every other rank (symmetric memory), and the decode GEMV's epilogue
+    # writes its slice into all of them; one small barrier kernel per layer stands where the all-gather stood.  Falls
+    # back to NCCL's all-gather when the mapping cannot be set up (or with --gather nccl).
+    push = None
+    if world > 1 and args.gather == "push":
+        try:
+            import torch.distributed._symmetric_memory as symm
+            y_arena = symm.empty(L * world * n_layer_local, dtype=torch.float32, device=dev)
+            y_hdl = symm.rendezvous(y_arena, dist.group.WORLD)
+            flags = symm.empty(64, dtype=torch.int32, device=dev)
+            flags.zero_()
+            f_hdl = symm.rendezvous(flags, dist.group.WORLD)
+            order = [rank] + [r for r in range(world) if r != rank]          # own buffer first
+            push = {"y_ptrs": [int(y_hdl.buffer_ptrs[r]) for r in order], "flag_ptrs": [int(p) for p in f_hdl.buffer_ptrs],
+                    "epoch": torch.zeros(1, dtype=torch.int32, device=dev), "status": torch.zeros(1, dtype=torch.int32, device=dev),
+                    "keep": (y_hdl, f_hdl, flags)}
+            torch.cuda.synchronize()
+            dist.barrier()
+        except Exception as e:      # noqa: BLE001 -- any failure of the mapping means the NCCL path
+            if rank == 0:
+                print("symmetric memory unavailable (%s: %s); using the NCCL all-gather" % (type(e).__name__, e), file=sys.stderr)
+            push = None
+    if push is None:
+        y_arena = torch.empty((L * world * n_layer_local,), device=dev, dtype=torch.float32)
     x_off = 0
     for layer in range(L):
         # the layer's seven local outputs sit side by side, so that one all-gather assembles the layer's output
         y_layer_all = y_arena[layer * world * n_layer_local:(layer + 1) * world * n_layer_local] if world > 1 else None
-        y_layer_loc = (torch.empty((n_layer_local,), device=dev, dtype=torch.float32) if world > 1
-                       else y_arena[layer * n_layer_local:(layer + 1) * n_layer_local])
+        if world == 1:
+            y_layer_loc = y_arena[layer * n_layer_local:(layer + 1) * n_layer_local]
+        elif push is not None:       # this rank's slot of the gathered layout, in place
+            y_layer_loc = y_layer_all[rank * n_layer_local:(rank + 1) * n_layer_local]
+        else:
+            y_layer_loc = torch.empty((n_layer_local,), device=dev, dtype=torch.float32)
         layer_bufs.append(y_layer_loc)
         col = 0
         for gi, names in enumerate(GROUPS):
@@ -204,24 +231,37 @@ def run_ours(args):
                 members.append((N, nl, w, y_loc, y_loc))
                 mats.append((K, N))
             last = gi == len(GROUPS) - 1
-            groups.append((K, x, rq.new_workspace(K, 1, dev), members, (y_layer_all, y_layer_loc) if (world > 1 and last) else None))
+            dst = None
+            if push is not None:      # element offset of each member's output inside every rank's arena
+                offs, c0 = [], col - sum(m[1] for m in members)
+                for m in members:
+                    offs.append((layer * world + rank) * n_layer_local + c0)
+                    c0 += m[1]
+                dst = [[base + 4 * o for o in offs] for base in push["y_ptrs"]]
+            groups.append((K, x, rq.new_workspace(K, 1, dev), members,
+                           (y_layer_all, y_layer_loc) if (world > 1 and last) else None, dst))
     torch.cuda.synchronize()
     # algorithmic bytes: every weight block and every output once, every activation once per group that shares it
-    total_bytes = sum(N * (K // 256) * 144 + 4 * N for (K, N) in mats) + sum(4 * K for (K, *_r) in groups)
+    total_bytes = sum(N * (K // 256) * 144 + 4 * N for (K, N) in mats) + sum(4 * g[0] for g in groups)
     stream = torch.cuda.Stream(device=dev)
 
     def enqueue_pass(quantize=True, layers=None):
         per_layer = len(GROUPS)
         sel = groups if layers is None else groups[layers[0] * per_layer:layers[1] * per_layer]
-        for K, x, ws, members, gather in sel:
+        for K, x, ws, members, gather, dst in sel:
             weights = [m[2] for m in members]
             outs = [m[3] for m in members]
-            if quantize:
+            if dst is not None:
+                rq.mul_mat_push(weights, x, dst, [m[1] for m in members], clip=1.0, act_group=64, workspace=ws, stream=stream)
+            elif quantize:
                 rq.mul_mat(weights, x, out=outs, clip=1.0, act_group=64, workspace=ws, stream=stream)
             else:
                 rq.mul_mat_quantized(weights, 1, ws, out=outs, act_group=64, stream=stream)
             if gather is not None:       # end of a layer: every rank gets every rank's slice of the layer's output
-                dist.all_gather_into_tensor(gather[0], gather[1])
+                if push is not None:
+                    rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
+                else:
+                    dist.all_gather_into_tensor(gather[0], gather[1])
 
     def capture(fn):
         g = torch.cuda.CUDAGraph()
@@ -233,6 +273,21 @@ def run_ours(args):
         return g
 
     g_pass = capture(lambda: enqueue_pass(True))
+    if push is not None:
+        # one pass has run (the capture's warm-up): the pushed arena must equal what NCCL's all-gather assembles from the
+        # ranks' own slots, bit for bit, and no barrier may have run out of time
+        torch.cuda.synchronize()
+        dist.barrier()
+        ya = y_arena.view(L, world, n_layer_local)
+        mine = ya[:, rank].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        ref_arena = torch.stack(parts, dim=1)
+        same = bool((ref_arena.view(torch.int32) == ya.view(torch.int32)).all().item()) and int(push["status"].item()) == 0
+        flag = torch.tensor([1 if same else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) != 1:
+            raise SystemExit("pushed outputs differ from the all-gathered ones (or a barrier timed out)")
     g_gemv = capture(lambda: enqueue_pass(False)) if world == 1 else None
 
     def barrier():
@@ -369,7 +424,10 @@ def run_ours(args):
                            "weights_gb": sum(N * (K // 256) * 144 for (K, N) in mats) / 1e9,
                            "activation_sharing": "q,k,v | o | gate,up | down: one rotate+quantize and one GEMV launch per group",
                            "l2": "inputs larger than L2 (weights streamed once per step)",
-                           "parallelism": "N-sharded x%d, one NCCL all-gather per layer output" % world if world > 1 else "single GPU",
+                           "parallelism": ("single GPU" if world == 1 else
+                                           "N-sharded x%d, GEMV epilogues store into every rank's output over NVLink, one barrier kernel "
+                                           "per layer (checked against an NCCL all-gather)" % world if push is not None else
+                                           "N-sharded x%d, one NCCL all-gather per layer output" % world),
                            "cuda_graph": True},
                 "frac_of_hbm_peak": value / (hbm_peak * world), "peak_kind": "of " + peak_kind,
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "prefill": prefill, "clocks": clocks,
@@ -514,6 +572,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--single", default="", help="K,N,M[,type]: time one shape instead of the stack")
     ap.add_argument("--wquant", default="", help="K,N[,type[,wgroup]]: time the GPU weight quantizer beside the reference's CPU code")
+    ap.add_argument("--gather", default="push", choices=["push", "nccl"], help="N > 1: how a layer's output is assembled")
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--group", type=int, default=64)
     ap.add_argument("--path", type=int, default=0)

@@ -48,6 +48,8 @@ typedef enum rq_status {
     RQ_ERR_LIMIT      = -10  /* a size beyond a stated fixed maximum */
 } rq_status;
 
+#define RQ_MAX_RANKS 8   /* ranks of one node whose output buffers a push call can address */
+
 /* which kernel-side layouts rq_w4a4_prepare builds */
 #define RQ_PREPACK_DECODE  1   /* int4 stream for the M <= 16 GEMV            (K*N/2 bytes) */
 #define RQ_PREPACK_PREFILL 2   /* int8 operand for the tcgen05 GEMM           (K*N bytes)   */
@@ -157,6 +159,22 @@ int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off
 /* Synchronises `stream` and returns RQ_OK or RQ_ERR_DEVICE if a kernel of an earlier call on this workspace gave
  * up on a bounded wait.  Not capture-safe. */
 int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream);
+
+/* N-sharded ranks of one node (the reference assembles the outputs with a collective after the node; here the node
+ * writes them itself).  rq_w4a4_mul_mat_push is rq_w4a4_mul_mat on the decode path (M <= 64, decode layout) whose epilogue
+ * stores every output value into n_dst buffers instead of one: y_dst[d * n_w + i] is weight i's output in destination d
+ * -- this rank's own buffer and the peer-mapped buffers of the other ranks (cudaIpc / symmetric memory), all with the
+ * same row stride ldy[i].  No collective kernel follows.  rq_rank_barrier then makes the pushed data of all ranks
+ * visible: rank r stores a fresh epoch into word r of every rank's flag array (flags_of_rank[p] = rank p's array of
+ * n_ranks words, peer-mapped, zero-initialised) and waits, bounded, until its own array shows that epoch from every
+ * rank; the epoch counts up in *epoch_dev (local device memory, zero-initialised), so a captured graph replays
+ * correctly.  On expiry of the wait *status_dev becomes 3 and the kernel returns.  One barrier kernel per GPU; ranks
+ * are separate processes or threads, one per GPU. */
+int rq_w4a4_mul_mat_push(const rq_weight_desc * const * w, int n_w, const float * x_dev, int64_t ldx, int64_t M,
+                         float * const * y_dst, int n_dst, const int64_t * ldy, float clip, int act_group,
+                         void * workspace_dev, size_t workspace_bytes, void * stream);
+int rq_rank_barrier(uint32_t * const * flags_of_rank, int rank, int n_ranks, uint32_t * epoch_dev, int32_t * status_dev,
+                    void * stream);
 
 /* The reference's weight quantizer on the GPU: N rows of K fp32 (rows ldw floats apart) -> N rows of K/256 blocks,
  * byte for byte what quantize_w4a4 / quantize_w4a4h write (patch:2775-2789; per row quantize_row_w4a4_ref /

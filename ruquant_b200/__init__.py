@@ -22,7 +22,7 @@ EXPORTS = [
     "rq_w4a4_prepare", "rq_w4a4_workspace_bytes", "rq_w4a4_mul_mat", "rq_w4a4_mul_mat_quantized", "rq_w4a4_rotate",
     "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
     "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n", "rq_w4a4_act_format",
-    "rq_w4a4_quantize_weights", "rq_w4a4_quantize_weights_scratch_bytes",
+    "rq_w4a4_quantize_weights", "rq_w4a4_quantize_weights_scratch_bytes", "rq_w4a4_mul_mat_push", "rq_rank_barrier",
 ]
 
 
@@ -75,6 +75,9 @@ def lib():
         L.rq_w4a4_rotate.argtypes = [vp, i64, i64, i64, i64, vp, i64, vp]
         L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, i32, vp, sz, vp]
         L.rq_w4a4_act_format.argtypes = [ctypes.POINTER(pd), i32, i64, i32]
+        L.rq_w4a4_mul_mat_push.argtypes = [ctypes.POINTER(pd), i32, vp, i64, i64, ctypes.POINTER(vp), i32, ctypes.POINTER(i64), f32,
+                                           i32, vp, sz, vp]
+        L.rq_rank_barrier.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vp, vp]
         L.rq_w4a4_quantize_weights_scratch_bytes.argtypes = [i32, i64, i64, i32]
         L.rq_w4a4_quantize_weights_scratch_bytes.restype = sz
         L.rq_w4a4_quantize_weights.argtypes = [vp, i64, i32, i64, i64, i32, i32, vp, vp, sz, vp]
@@ -191,6 +194,38 @@ def mul_mat(weights, x, out=None, clip=None, act_group=None, path=PATH_AUTO, wor
         _check(lib().rq_w4a4_mul_mat(descs, n_w, x.data_ptr(), x.stride(0), M, ys, ldy, clip, act_group, path,
                                      workspace.data_ptr(), workspace.numel(), _stream_ptr(stream)), "rq_w4a4_mul_mat")
     return outs[0] if single else outs
+
+
+def mul_mat_push(weights, x, dst_ptrs, ldy, clip=None, act_group=None, workspace=None, stream=None):
+    """The decode-path node writing every output into several buffers: dst_ptrs[d][i] is the device address of weight
+    i's output in destination d (this rank's own buffer first, then the peer-mapped buffers of the other ranks)."""
+    import torch
+    ws_list = [weights] if isinstance(weights, Weight) else list(weights)
+    n_w, n_dst = len(ws_list), len(dst_ptrs)
+    K, M = ws_list[0].K, x.shape[0]
+    if clip is None:
+        clip = ws_list[0].clip()
+    if act_group is None:
+        act_group = lib().rq_w4a4_act_group()
+    with torch.cuda.device(x.device):
+        if workspace is None:
+            workspace = new_workspace(K, M, x.device)
+        pd = ctypes.POINTER(WeightDesc)
+        descs = (pd * n_w)(*[ctypes.pointer(w.desc) for w in ws_list])
+        ys = (ctypes.c_void_p * (n_w * n_dst))(*[dst_ptrs[d][i] for d in range(n_dst) for i in range(n_w)])
+        lds = (ctypes.c_int64 * n_w)(*ldy)
+        _check(lib().rq_w4a4_mul_mat_push(descs, n_w, x.data_ptr(), x.stride(0), M, ys, n_dst, lds, clip, act_group,
+                                          workspace.data_ptr(), workspace.numel(), _stream_ptr(stream)), "rq_w4a4_mul_mat_push")
+    return workspace
+
+
+def rank_barrier(flag_ptrs, rank, epoch, status=None, stream=None):
+    """flag_ptrs[p]: device address (as mapped on this rank) of rank p's flag array; epoch: a zero-initialised uint32
+    tensor on this device; status: an int32 tensor that becomes 3 if the bounded wait expires."""
+    n = len(flag_ptrs)
+    arr = (ctypes.c_void_p * n)(*flag_ptrs)
+    _check(lib().rq_rank_barrier(arr, rank, n, epoch.data_ptr(), status.data_ptr() if status is not None else None,
+                                 _stream_ptr(stream)), "rq_rank_barrier")
 
 
 def mul_mat_static(weight, x, out=None, clip=None, act_group=None, path=PATH_AUTO, stream=None):

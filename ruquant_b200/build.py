@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.environ.get("RQ_B200_LIB") or os.path.join(HERE, "librq_b200.so")
-SOURCES = ["rq_api.cu", "rq_act.cu", "rq_prepack.cu", "rq_gemv.cu", "rq_gemm_tc.cu", "rq_static.cu", "rq_wquant.cu"]
+SOURCES = ["rq_api.cu", "rq_act.cu", "rq_prepack.cu", "rq_gemv.cu", "rq_gemm_tc.cu", "rq_static.cu", "rq_wquant.cu", "rq_rank.cu"]
 NVCC_FLAGS = ["-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-cudart", "static"]
 

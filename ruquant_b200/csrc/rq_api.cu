@@ -328,7 +328,7 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(
         RQ_CUDA(rq_launch_gemm_tc(w->tmap_w8, sw, w->wk_mode ? RQ_FMT_I8 : RQ_FMT_E4M3, w->K, w->N, a8, msh, u, M, act_group, y_dev, ldy, status, stream));
     } else {
         rq_gemv_job job;
-        job.w4 = pp + w->off_w4; job.sw = sw; job.N = w->N; job.y = y_dev; job.ldy = ldy;
+        job.w4 = pp + w->off_w4; job.sw = sw; job.N = w->N; job.y = y_dev; job.ldy = ldy; job.n_more = 0;
         job.wk = w->wk_mode ? reinterpret_cast<const int8_t *>(pp + w->off_wk) : nullptr;
         RQ_CUDA(rq_launch_gemv(&job, 1, w->K, a8, msh, u, M, act_group, status, stream));
     }
@@ -363,7 +363,7 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized_
             jobs[i].w4 = pp + w[i]->off_w4;
             jobs[i].sw = reinterpret_cast<const float *>(pp + w[i]->off_sw);
             jobs[i].wk = w[i]->wk_mode ? reinterpret_cast<const int8_t *>(pp + w[i]->off_wk) : nullptr;
-            jobs[i].N = w[i]->N; jobs[i].y = y_dev[i]; jobs[i].ldy = ldy[i];
+            jobs[i].N = w[i]->N; jobs[i].y = y_dev[i]; jobs[i].ldy = ldy[i]; jobs[i].n_more = 0;
         }
         RQ_CUDA(rq_launch_gemv(jobs, n_w, w[0]->K, reinterpret_cast<const int8_t *>(ws + l.off_a8),
                                reinterpret_cast<const int32_t *>(ws + l.off_msh), reinterpret_cast<const float *>(ws + l.off_u), M,
@@ -392,6 +392,51 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat(const rq_w
                               workspace_dev, workspace_bytes, stream);
     if (rc != RQ_OK) return rc;
     return rq_w4a4_mul_mat_quantized_n(w, n_w, M, y_dev, ldy, act_group, path, workspace_dev, workspace_bytes, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_push(const rq_weight_desc * const * w, int n_w, const float * x_dev, int64_t ldx,
+                                    int64_t M, float * const * y_dst, int n_dst, const int64_t * ldy, float clip,
+                                    int act_group, void * workspace_dev, size_t workspace_bytes, void * stream) {
+    if (w == nullptr || y_dst == nullptr || ldy == nullptr || n_w < 1 || n_w > RQ_MAX_WEIGHTS || n_dst < 1 || n_dst > RQ_MAX_RANKS)
+        return RQ_ERR_ARG;
+    if (M < 1) return RQ_ERR_SHAPE;
+    if (M > 64) return RQ_ERR_LIMIT;
+    for (int i = 0; i < n_w; ++i) {
+        if (w[i] == nullptr) return RQ_ERR_ARG;
+        if (w[i]->K != w[0]->K || w[i]->type != w[0]->type || w[i]->n_rot != w[0]->n_rot || w[i]->wk_mode != w[0]->wk_mode)
+            return RQ_ERR_MISMATCH;
+        if ((w[i]->layouts & RQ_PREPACK_DECODE) == 0 || w[i]->prepack == nullptr || ldy[i] < w[i]->N) return RQ_ERR_ARG;
+        if (w[i]->wg64 && act_group != 64) return RQ_ERR_GROUP;
+        for (int d = 0; d < n_dst; ++d) if (y_dst[d * n_w + i] == nullptr) return RQ_ERR_ARG;
+    }
+    int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group, RQ_FMT_I8,
+                              workspace_dev, workspace_bytes, stream);
+    if (rc != RQ_OK) return rc;
+    const rq_ws_layout l = rq_ws(w[0]->K, M);
+    uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
+    rq_gemv_job jobs[RQ_MAX_WEIGHTS];
+    for (int i = 0; i < n_w; ++i) {
+        const uint8_t * pp = static_cast<const uint8_t *>(w[i]->prepack);
+        jobs[i].w4 = pp + w[i]->off_w4;
+        jobs[i].sw = reinterpret_cast<const float *>(pp + w[i]->off_sw);
+        jobs[i].wk = w[i]->wk_mode ? reinterpret_cast<const int8_t *>(pp + w[i]->off_wk) : nullptr;
+        jobs[i].N = w[i]->N; jobs[i].y = y_dst[i]; jobs[i].ldy = ldy[i];
+        jobs[i].n_more = n_dst - 1;
+        for (int d = 1; d < n_dst; ++d) jobs[i].y_more[d - 1] = y_dst[d * n_w + i];
+    }
+    RQ_CUDA(rq_launch_gemv(jobs, n_w, w[0]->K, reinterpret_cast<const int8_t *>(ws + l.off_a8),
+                           reinterpret_cast<const int32_t *>(ws + l.off_msh), reinterpret_cast<const float *>(ws + l.off_u), M,
+                           act_group, reinterpret_cast<int32_t *>(ws + l.off_status), (cudaStream_t) stream));
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_rank_barrier(uint32_t * const * flags_of_rank, int rank, int n_ranks, uint32_t * epoch_dev,
+                               int32_t * status_dev, void * stream) {
+    if (flags_of_rank == nullptr || epoch_dev == nullptr || n_ranks < 1 || n_ranks > RQ_MAX_RANKS || rank < 0 || rank >= n_ranks)
+        return RQ_ERR_ARG;
+    for (int p = 0; p < n_ranks; ++p) if (flags_of_rank[p] == nullptr) return RQ_ERR_ARG;
+    RQ_CUDA(rq_launch_rank_barrier(flags_of_rank, rank, n_ranks, epoch_dev, status_dev, (cudaStream_t) stream));
+    return RQ_OK;
 }
 
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream) {

@@ -133,12 +133,17 @@ struct rq_gemv_job {
     int64_t N;
     float * y;
     int64_t ldy;
+    float * y_more[RQ_MAX_RANKS - 1];   // further destinations of the same output (peer-mapped buffers of other ranks)
+    int n_more;
 };
 cudaError_t rq_launch_gemv(const rq_gemv_job * jobs, int n_jobs, int64_t K, const int8_t * a8, const int32_t * msh,
                            const float * u, int64_t M, int G, int32_t * status, cudaStream_t stream);
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
+// all-ranks barrier over peer-mapped flag words (rq_rank.cu)
+cudaError_t rq_launch_rank_barrier(uint32_t * const * flags_of_rank, int rank, int n_ranks, uint32_t * epoch, int32_t * status,
+                                   cudaStream_t stream);
 // weight quantizer: scale search + pack of already-rotated rows (rq_wquant.cu)
 cudaError_t rq_launch_wquant(const float * x, int64_t ldx, int64_t n_rows, int64_t K, int wgroup, int pad0, float * sg,
                              rq_block * out, cudaStream_t stream);

@@ -33,8 +33,10 @@ struct GemvJob {            // one weight of the launch
     const float * sw;
     const int8_t * wk;      // [N][K/64] or null
     float * y;
+    float * y_more[RQ_MAX_RANKS - 1];   // further copies of the output (other ranks' buffers, peer-mapped), same layout
     int64_t ldy;
     int N;
+    int n_more;
 };
 
 // Up to three weights that share the activation (q/k/v, gate/up) are one launch: their row tiles form one list
@@ -90,8 +92,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // the weights do not depend on the preceding kernel, and it never drains between tiles); the consumer warps take the
 // chunks of that stream round-robin, so 64 KB per CTA stay in flight or resident from the first cycle to the last.
 // NT: token tiles of 8 (1 or 2).  GS: 64-input steps per activation group (1, 2, 4).  HAS_K: weight multipliers.
-// ONE: M == 1 (only token 0 is folded and stored).
-template <int NT, int GS, bool HAS_K, bool ONE>
+// ONE: M == 1 (only token 0 is folded and stored).  PUSH: outputs also go to the jobs' further destinations.
+template <int NT, int GS, bool HAS_K, bool ONE, bool PUSH>
 __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const GemvParams prm) {
     extern __shared__ __align__(128) uint8_t dyn[];
     __shared__ uint64_t full[STAGES], empty[STAGES];
@@ -318,8 +320,17 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                 const int tok = 8 * t + 2 * tig + c;
                 if (tok < M && fmt_ok) {
                     const float ut = __ldg(prm.u + tok);
-                    if (row_lo < jb.N) jb.y[(size_t) tok * jb.ldy + row_lo] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][c], 16.0f), ut), s_lo);
-                    if (row_hi < jb.N) jb.y[(size_t) tok * jb.ldy + row_hi] = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][2 + c], 16.0f), ut), s_hi);
+                    const float v_lo = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][c], 16.0f), ut), s_lo);
+                    const float v_hi = __fmul_rn(__fmul_rn(__fmul_rn((float) tot[t][2 + c], 16.0f), ut), s_hi);
+                    if (row_lo < jb.N) jb.y[(size_t) tok * jb.ldy + row_lo] = v_lo;
+                    if (row_hi < jb.N) jb.y[(size_t) tok * jb.ldy + row_hi] = v_hi;
+                    // N-sharded ranks: the same values straight into every other rank's copy of the output
+                    if constexpr (PUSH) {
+                    for (int d = 0; d < jb.n_more; ++d) {
+                        if (row_lo < jb.N) jb.y_more[d][(size_t) tok * jb.ldy + row_lo] = v_lo;
+                        if (row_hi < jb.N) jb.y_more[d][(size_t) tok * jb.ldy + row_hi] = v_hi;
+                    }
+                    }
                 }
             }
         }
@@ -327,7 +338,7 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
     if (threadIdx.x == 0) rq_trace(prm.status, 0x13);
 }
 
-template <int NT, int GS, bool HAS_K, bool ONE>
+template <int NT, int GS, bool HAS_K, bool ONE, bool PUSH>
 cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
     static bool configured[64] = {};
     static int per_sm[64] = {};
@@ -336,11 +347,11 @@ cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(rq_gemv_mma_kernel<NT, GS, HAS_K, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        e = cudaFuncSetAttribute(rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return e;
         // persistent grid: as many CTAs as are resident at once
         int nb = 0, sms = 148;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE>, (CONSUMERS + 1) * 32, smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, (CONSUMERS + 1) * 32, smem);
         if (e != cudaSuccess) return e;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         per_sm[dev] = (nb > 0 ? nb : 1) * sms;
@@ -361,13 +372,15 @@ cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = getenv("RQ_NO_PDL") ? 0 : 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE>, prm);
+    return cudaLaunchKernelEx(&cfg, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, prm);
 }
 
 template <int NT, int GS, bool HAS_K>
 cudaError_t launch(const GemvParams & prm, cudaStream_t stream) {
-    if (NT == 1 && prm.M == 1) return launch_one<1, GS, HAS_K, true>(prm, stream);
-    return launch_one<NT, GS, HAS_K, false>(prm, stream);
+    bool push = false;
+    for (int i = 0; i < prm.n_jobs; ++i) push = push || prm.job[i].n_more > 0;
+    if (NT == 1 && prm.M == 1) return push ? launch_one<1, GS, HAS_K, true, true>(prm, stream) : launch_one<1, GS, HAS_K, true, false>(prm, stream);
+    return push ? launch_one<NT, GS, HAS_K, false, true>(prm, stream) : launch_one<NT, GS, HAS_K, false, false>(prm, stream);
 }
 
 template <int NT>
@@ -398,6 +411,8 @@ cudaError_t rq_launch_gemv(const rq_gemv_job * jobs, int n_jobs, int64_t K, cons
             prm.job[i].sw = jobs[i].sw;
             prm.job[i].wk = jobs[i].wk;
             prm.job[i].y = jobs[i].y + t0 * jobs[i].ldy;
+            prm.job[i].n_more = jobs[i].n_more;
+            for (int d = 0; d < jobs[i].n_more; ++d) prm.job[i].y_more[d] = jobs[i].y_more[d] + t0 * jobs[i].ldy;
             prm.job[i].ldy = jobs[i].ldy;
             prm.job[i].N = (int) jobs[i].N;
             prm.tile_start[i + 1] = prm.tile_start[i] + (int) ((jobs[i].N + 15) / 16);

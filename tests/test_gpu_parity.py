@@ -363,3 +363,42 @@ def test_column_split_needs_rotation_blocks(rq, port):
     with pytest.raises(rq.RqError) as e:
         rq.Weight(dev(cols).view(-1), 45, K // 2, N=N)
     assert e.value.status == -3
+
+
+# ------------------------------------------------------------------------------------------- push to several buffers
+
+def test_push_writes_every_destination(rq, port):
+    """rq_w4a4_mul_mat_push: the decode node storing its outputs into several buffers (other ranks' copies of Y); here all
+    destinations live on one GPU.  Three weights sharing x, strided destinations, bits against the oracle."""
+    K, M = 5120, 3
+    Ns = [96, 32, 48]
+    wbs = [port.quantize_weights(inputs.normal_weights(n, K, 9400 + i), 45) for i, n in enumerate(Ns)]
+    ws = [rq.Weight(dev(wb).view(-1), 45, K, N=n, layouts=rq.PREPACK_DECODE) for wb, n in zip(wbs, Ns)]
+    x = inputs.outlier_activations(M, K, 9410)
+    total = sum(Ns)
+    bufs = [torch.full((M, total + 8), -1.0, dtype=torch.float32, device="cuda") for _ in range(3)]
+    cols = np.concatenate([[0], np.cumsum(Ns)[:-1]])
+    dst = [[b.data_ptr() + 4 * int(c) for c in cols] for b in bufs]
+    rq.mul_mat_push(ws, dev(x), dst, [total + 8] * 3)
+    torch.cuda.synchronize()
+    want = np.concatenate([port.mul_mat(wb, 45, K, x) for wb in wbs], axis=1)
+    for b in bufs:
+        got = b.cpu().numpy()
+        assert_bits(got[:, :total], want, "push destination")
+        assert (got[:, total:] == -1.0).all()
+
+
+def test_rank_barrier_single_rank_and_expiry(rq):
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(3):                       # one rank: the kernel sees its own flag at once; the epoch counts up
+        rq.rank_barrier([flags.data_ptr()], 0, epoch, status)
+    torch.cuda.synchronize()
+    assert int(epoch.item()) == 3 and int(flags[0].item()) == 3 and int(status.item()) == 0
+    # two ranks, the other one never arrives: the bounded wait runs out, the status word says so, the context lives on
+    other = torch.zeros(8, dtype=torch.int32, device="cuda")
+    rq.rank_barrier([flags.data_ptr(), other.data_ptr()], 0, epoch, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 3 and int(other[0].item()) == 4
+    assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
