@@ -179,6 +179,12 @@ def run_ours(args):
     # back to NCCL's all-gather when the mapping cannot be set up (or with --gather nccl).
     push = None
     if world > 1 and args.gather == "push":
+        def all_agree(ok):      # a collective yes/no, so that the ranks never part ways
+            flag = torch.tensor([1 if ok else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            return int(flag.item()) == 1
+
+        why = ""
         try:
             import torch.distributed._symmetric_memory as symm
             y_arena = symm.empty(L * world * n_layer_local, dtype=torch.float32, device=dev)
@@ -191,11 +197,35 @@ def run_ours(args):
                     "epoch": torch.zeros(1, dtype=torch.int32, device=dev), "status": torch.zeros(1, dtype=torch.int32, device=dev),
                     "keep": (y_hdl, f_hdl, flags)}
             torch.cuda.synchronize()
-            dist.barrier()
         except Exception as e:      # noqa: BLE001 -- any failure of the mapping means the NCCL path
-            if rank == 0:
-                print("symmetric memory unavailable (%s: %s); using the NCCL all-gather" % (type(e).__name__, e), file=sys.stderr)
+            why, push = "%s: %s" % (type(e).__name__, e), None
+        if not all_agree(push is not None):
             push = None
+        if push is not None:
+            # pre-flight on a tiny weight: every rank pushes 32 outputs into slot `rank` of every arena, meets the others
+            # at the barrier kernel and must then hold what an NCCL all-gather of the same slices gives
+            ran = True
+            try:
+                tw = rq.Weight(synth.random_weights(32, 256, rq.TYPE_W4A4, seed=5 + rank, device=dev).view(-1), rq.TYPE_W4A4, 256,
+                               N=32, layouts=rq.PREPACK_DECODE)
+                tx = torch.ones((1, 256), device=dev, dtype=torch.float32)
+                rq.mul_mat_push([tw], tx, [[base + 4 * 32 * rank] for base in push["y_ptrs"]], [32], clip=1.0, act_group=64)
+                rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"])
+                torch.cuda.synchronize()
+            except Exception as e:      # noqa: BLE001
+                why, ran = "%s: %s" % (type(e).__name__, e), False
+            if all_agree(ran):
+                mine = y_arena[32 * rank:32 * rank + 32].clone()
+                parts = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(parts, mine)
+                good = int(push["status"].item()) == 0 and bool(
+                    (torch.cat(parts).view(torch.int32) == y_arena[:32 * world].view(torch.int32)).all().item())
+                if not all_agree(good):
+                    why, push = "pre-flight of the pushed outputs disagreed with the all-gather", None
+            else:
+                push = None
+        if push is None and rank == 0:
+            print("pushed outputs unavailable (%s); using the NCCL all-gather" % why, file=sys.stderr)
     if push is None:
         y_arena = torch.empty((L * world * n_layer_local,), device=dev, dtype=torch.float32)
     x_off = 0
