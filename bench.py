@@ -195,7 +195,7 @@ def run_ours(args):
             order = [rank] + [r for r in range(world) if r != rank]          # own buffer first
             push = {"y_ptrs": [int(y_hdl.buffer_ptrs[r]) for r in order], "flag_ptrs": [int(p) for p in f_hdl.buffer_ptrs],
                     "epoch": torch.zeros(1, dtype=torch.int32, device=dev), "status": torch.zeros(1, dtype=torch.int32, device=dev),
-                    "keep": (y_hdl, f_hdl, flags)}
+                    "keep": (y_hdl, f_hdl, flags), "symm": symm, "order": order}
             torch.cuda.synchronize()
         except Exception as e:      # noqa: BLE001 -- any failure of the mapping means the NCCL path
             why, push = "%s: %s" % (type(e).__name__, e), None
@@ -412,10 +412,22 @@ def run_ours(args):
             g.manual_seed(99)
             x = torch.randn((M, K), generator=g, device=dev, dtype=torch.float32)
             y = torch.empty((M, nl), device=dev, dtype=torch.float32)
-            y_all = torch.empty((world, M, nl), device=dev, dtype=torch.float32) if world > 1 else None
             ws = rq.new_workspace(K, M, dev)
+            y_all, dst = None, None
+            if world > 1 and push is not None:
+                # the gathered [M][N] output of every rank, mapped everywhere: the GEMM's final store writes this rank's
+                # columns into all of them while the MMAs of the next unit run; then one barrier kernel
+                y_all = push["symm"].empty(M * N, dtype=torch.float32, device=dev)
+                hdl = push["symm"].rendezvous(y_all, dist.group.WORLD)
+                dst = [[int(hdl.buffer_ptrs[r]) + 4 * rank * nl] for r in push["order"]]
+            elif world > 1:
+                y_all = torch.empty((world, M, nl), device=dev, dtype=torch.float32)
 
             def node():
+                if dst is not None:
+                    rq.mul_mat_push([w], x, dst, [N], clip=1.0, act_group=64, workspace=ws, stream=stream)
+                    rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
+                    return
                 rq.mul_mat(w, x, out=y, clip=1.0, act_group=64, workspace=ws, stream=stream)
                 if world > 1:
                     dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
@@ -424,6 +436,21 @@ def run_ours(args):
                 rq.mul_mat_quantized(w, M, ws, out=y, act_group=64, stream=stream)
 
             ms_node = timed(node, max(3, args.steps), 3)
+            if dst is not None:
+                # the pushed [M][N] must hold, in this rank's columns, what the plain node computes, on every rank
+                torch.cuda.synchronize()
+                dist.barrier()
+                with torch.cuda.stream(stream):
+                    rq.mul_mat(w, x, out=y, clip=1.0, act_group=64, workspace=ws, stream=stream)
+                stream.synchronize()
+                parts = [torch.empty_like(y) for _ in range(world)]
+                dist.all_gather(parts, y)
+                same = bool((torch.cat(parts, dim=1).view(torch.int32) == y_all.view(M, N).view(torch.int32)).all().item())
+                same = same and int(push["status"].item()) == 0
+                flag = torch.tensor([1 if same else 0], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if int(flag.item()) != 1:
+                    raise SystemExit("prefill: pushed output differs from the all-gathered one")
             ms_gemm = timed(gemm_only, max(3, args.steps), 3)
             rq.device_status(ws, K, M)
             ops = 2.0 * M * N * K

@@ -161,8 +161,8 @@ int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off
 int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream);
 
 /* N-sharded ranks of one node (the reference assembles the outputs with a collective after the node; here the node
- * writes them itself).  rq_w4a4_mul_mat_push is rq_w4a4_mul_mat on the decode path (M <= 64, decode layout) whose epilogue
- * stores every output value into n_dst buffers instead of one: y_dst[d * n_w + i] is weight i's output in destination d
+ * writes them itself).  rq_w4a4_mul_mat_push is rq_w4a4_mul_mat (GEMV up to 64 tokens: needs the decode layout; tcgen05
+ * kernel above: needs the prefill layout) whose epilogue stores every output value into n_dst buffers instead of one: y_dst[d * n_w + i] is weight i's output in destination d
  * -- this rank's own buffer and the peer-mapped buffers of the other ranks (cudaIpc / symmetric memory), all with the
  * same row stride ldy[i].  No collective kernel follows.  rq_rank_barrier then makes the pushed data of all ranks
  * visible: rank r stores a fresh epoch into word r of every rank's flag array (flags_of_rank[p] = rank p's array of

@@ -400,20 +400,34 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_push(const
     if (w == nullptr || y_dst == nullptr || ldy == nullptr || n_w < 1 || n_w > RQ_MAX_WEIGHTS || n_dst < 1 || n_dst > RQ_MAX_RANKS)
         return RQ_ERR_ARG;
     if (M < 1) return RQ_ERR_SHAPE;
-    if (M > 64) return RQ_ERR_LIMIT;
+    const bool tc = M > 64;          // wider inputs: the tcgen05 kernel's final store pushes instead
     for (int i = 0; i < n_w; ++i) {
         if (w[i] == nullptr) return RQ_ERR_ARG;
         if (w[i]->K != w[0]->K || w[i]->type != w[0]->type || w[i]->n_rot != w[0]->n_rot || w[i]->wk_mode != w[0]->wk_mode)
             return RQ_ERR_MISMATCH;
-        if ((w[i]->layouts & RQ_PREPACK_DECODE) == 0 || w[i]->prepack == nullptr || ldy[i] < w[i]->N) return RQ_ERR_ARG;
+        if ((w[i]->layouts & (tc ? RQ_PREPACK_PREFILL : RQ_PREPACK_DECODE)) == 0 || w[i]->prepack == nullptr || ldy[i] < w[i]->N)
+            return RQ_ERR_ARG;
         if (w[i]->wg64 && act_group != 64) return RQ_ERR_GROUP;
         for (int d = 0; d < n_dst; ++d) if (y_dst[d * n_w + i] == nullptr) return RQ_ERR_ARG;
     }
-    int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group, RQ_FMT_I8,
+    const int fmt = tc && !w[0]->wk_mode ? RQ_FMT_E4M3 : RQ_FMT_I8;
+    int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group, fmt,
                               workspace_dev, workspace_bytes, stream);
     if (rc != RQ_OK) return rc;
     const rq_ws_layout l = rq_ws(w[0]->K, M);
     uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
+    if (tc) {
+        for (int i = 0; i < n_w; ++i) {
+            const uint8_t * pp = static_cast<const uint8_t *>(w[i]->prepack);
+            float * more[RQ_MAX_RANKS - 1];
+            for (int d = 1; d < n_dst; ++d) more[d - 1] = y_dst[d * n_w + i];
+            RQ_CUDA(rq_launch_gemm_tc(w[i]->tmap_w8, reinterpret_cast<const float *>(pp + w[i]->off_sw), fmt, w[i]->K, w[i]->N,
+                                      reinterpret_cast<const int8_t *>(ws + l.off_a8), reinterpret_cast<const int32_t *>(ws + l.off_msh),
+                                      reinterpret_cast<const float *>(ws + l.off_u), M, act_group, y_dst[i], ldy[i],
+                                      reinterpret_cast<int32_t *>(ws + l.off_status), (cudaStream_t) stream, more, n_dst - 1));
+        }
+        return RQ_OK;
+    }
     rq_gemv_job jobs[RQ_MAX_WEIGHTS];
     for (int i = 0; i < n_w; ++i) {
         const uint8_t * pp = static_cast<const uint8_t *>(w[i]->prepack);

@@ -140,7 +140,8 @@ cudaError_t rq_launch_gemv(const rq_gemv_job * jobs, int n_jobs, int64_t K, cons
                            const float * u, int64_t M, int G, int32_t * status, cudaStream_t stream);
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
-                              float * y, int64_t ldy, int32_t * status, cudaStream_t stream);
+                              float * y, int64_t ldy, int32_t * status, cudaStream_t stream, float * const * y_more = nullptr,
+                              int n_more = 0);
 // all-ranks barrier over peer-mapped flag words (rq_rank.cu)
 cudaError_t rq_launch_rank_barrier(uint32_t * const * flags_of_rank, int rank, int n_ranks, uint32_t * epoch, int32_t * status,
                                    cudaStream_t stream);

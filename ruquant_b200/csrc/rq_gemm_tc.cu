@@ -206,9 +206,11 @@ struct TcParams {
     const int32_t * msh;
     const float * u;
     float * y;
+    float * y_more[RQ_MAX_RANKS - 1];   // further copies of the output (other ranks' buffers, peer-mapped), same layout
     int64_t ldy;
     int32_t * status;
     int K, N, M, G;
+    int n_more;
 };
 
 struct __align__(8) TcShared {
@@ -224,7 +226,7 @@ struct __align__(8) TcShared {
 // m_unit -- token tiles fastest, so the CTAs running at one time share their weight slices in L2.  Slots, phases and
 // accumulator buffers are running counters that carry over from one unit to the next: the MMAs of the next unit start
 // while the epilogue warps still scale and store the previous one.
-template <bool F8, bool PAIR>
+template <bool F8, bool PAIR, bool PUSH>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams prm) {
     constexpr int STAGES = stages_of(PAIR);
@@ -527,14 +529,18 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         const float4 q = *reinterpret_cast<const float4 *>(stg + rr * 32 + ((jj ^ (rr & 7)) << 2));
                         const float o0 = __fmul_rn(q.x, sc[0]), o1 = __fmul_rn(q.y, sc[1]), o2 = __fmul_rn(q.z, sc[2]), o3 = __fmul_rn(q.w, sc[3]);
                         if (grow < prm.M) {
-                            float * yr = prm.y + (size_t) grow * prm.ldy + ncol;
-                            if (vec && ncol + 3 < prm.N) {
-                                *reinterpret_cast<float4 *>(yr) = make_float4(o0, o1, o2, o3);
-                            } else {
-                                if (ncol < prm.N) yr[0] = o0;
-                                if (ncol + 1 < prm.N) yr[1] = o1;
-                                if (ncol + 2 < prm.N) yr[2] = o2;
-                                if (ncol + 3 < prm.N) yr[3] = o3;
+                            // destination 0 is this GPU's buffer; N-sharded ranks get the same 128-byte row pieces straight
+                            // into their copies of the output while the MMAs of the next unit run
+                            for (int dd = 0; dd <= (PUSH ? prm.n_more : 0); ++dd) {
+                                float * yr = (!PUSH || dd == 0 ? prm.y : prm.y_more[dd - 1]) + (size_t) grow * prm.ldy + ncol;
+                                if (vec && ncol + 3 < prm.N) {
+                                    *reinterpret_cast<float4 *>(yr) = make_float4(o0, o1, o2, o3);
+                                } else {
+                                    if (ncol < prm.N) yr[0] = o0;
+                                    if (ncol + 1 < prm.N) yr[1] = o1;
+                                    if (ncol + 2 < prm.N) yr[2] = o2;
+                                    if (ncol + 3 < prm.N) yr[3] = o3;
+                                }
                             }
                         }
                     }
@@ -592,16 +598,25 @@ int rq_encode_tmap_i8(void * tmap_out, const void * base, int64_t K, int64_t row
     return 0;
 }
 
-cudaError_t rq_configure_gemm_tc() {
-    // <F8, PAIR>: fp8 operands (no weight multipliers) or int8; single CTAs or pairs
-    cudaError_t e;
-    if ((e = cudaFuncSetAttribute(rq_gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_of(false))) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(rq_gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_of(false))) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(rq_gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_of(true))) != cudaSuccess) return e;
-    return cudaFuncSetAttribute(rq_gemm_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_of(true));
+template <bool F8, bool PAIR, bool PUSH>
+static cudaError_t configure_tc() {
+    return cudaFuncSetAttribute(rq_gemm_tc_kernel<F8, PAIR, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_of(PAIR));
 }
 
-template <bool F8, bool PAIR>
+cudaError_t rq_configure_gemm_tc() {
+    // <F8, PAIR, PUSH>: fp8 operands (no weight multipliers) or int8; single CTAs or pairs; one or several destinations
+    cudaError_t e;
+    if ((e = configure_tc<false, false, false>()) != cudaSuccess) return e;
+    if ((e = configure_tc<true, false, false>()) != cudaSuccess) return e;
+    if ((e = configure_tc<false, true, false>()) != cudaSuccess) return e;
+    if ((e = configure_tc<true, true, false>()) != cudaSuccess) return e;
+    if ((e = configure_tc<false, false, true>()) != cudaSuccess) return e;
+    if ((e = configure_tc<true, false, true>()) != cudaSuccess) return e;
+    if ((e = configure_tc<false, true, true>()) != cudaSuccess) return e;
+    return configure_tc<true, true, true>();
+}
+
+template <bool F8, bool PAIR, bool PUSH>
 static cudaError_t launch_tc(const CUtensorMap & ta, const CUtensorMap & tb, const TcParams & prm, int sms, cudaStream_t stream) {
     const int m_tiles = (prm.M + BM - 1) / BM, n_tiles = (prm.N + BN - 1) / BN;
     const int units = (PAIR ? (m_tiles + 1) / 2 : m_tiles) * n_tiles;
@@ -619,12 +634,12 @@ static cudaError_t launch_tc(const CUtensorMap & ta, const CUtensorMap & tb, con
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, rq_gemm_tc_kernel<F8, PAIR>, ta, tb, prm);
+    return cudaLaunchKernelEx(&cfg, rq_gemm_tc_kernel<F8, PAIR, PUSH>, ta, tb, prm);
 }
 
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
-                              float * y, int64_t ldy, int32_t * status, cudaStream_t stream) {
+                              float * y, int64_t ldy, int32_t * status, cudaStream_t stream, float * const * y_more, int n_more) {
     static bool configured[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -644,8 +659,15 @@ cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, i
     TcParams prm;
     prm.sw = sw; prm.msh = msh; prm.u = u; prm.y = y; prm.ldy = ldy; prm.status = status;
     prm.K = (int) K; prm.N = (int) N; prm.M = (int) M; prm.G = G;
+    prm.n_more = n_more;
+    for (int d = 0; d < RQ_MAX_RANKS - 1; ++d) prm.y_more[d] = d < n_more ? y_more[d] : nullptr;
     static const int no_pair = getenv("RQ_TUNE_TC_NOPAIR") ? atoi(getenv("RQ_TUNE_TC_NOPAIR")) : 0;
     const bool pair = M > BM && !no_pair;      // a second token tile exists: let two CTAs share the weight slices
-    if (fmt == RQ_FMT_E4M3) return pair ? launch_tc<true, true>(ta, tb, prm, sms, stream) : launch_tc<true, false>(ta, tb, prm, sms, stream);
-    return pair ? launch_tc<false, true>(ta, tb, prm, sms, stream) : launch_tc<false, false>(ta, tb, prm, sms, stream);
+    const bool f8 = fmt == RQ_FMT_E4M3;
+    if (n_more > 0) {
+        if (f8) return pair ? launch_tc<true, true, true>(ta, tb, prm, sms, stream) : launch_tc<true, false, true>(ta, tb, prm, sms, stream);
+        return pair ? launch_tc<false, true, true>(ta, tb, prm, sms, stream) : launch_tc<false, false, true>(ta, tb, prm, sms, stream);
+    }
+    if (f8) return pair ? launch_tc<true, true, false>(ta, tb, prm, sms, stream) : launch_tc<true, false, false>(ta, tb, prm, sms, stream);
+    return pair ? launch_tc<false, true, false>(ta, tb, prm, sms, stream) : launch_tc<false, false, false>(ta, tb, prm, sms, stream);
 }

@@ -402,3 +402,19 @@ def test_rank_barrier_single_rank_and_expiry(rq):
     torch.cuda.synchronize()
     assert int(status.item()) == 3 and int(other[0].item()) == 4
     assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
+
+
+def test_push_from_the_tcgen05_kernel(rq, port):
+    """Above 64 tokens the push variant runs the tcgen05 kernel, whose final store writes every destination."""
+    K, N, M = 1024, 320, 200
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9500), 45)
+    w = rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    x = inputs.outlier_activations(M, K, 9501)
+    bufs = [torch.full((M, 2 * N), -1.0, dtype=torch.float32, device="cuda") for _ in range(2)]
+    rq.mul_mat_push([w], dev(x), [[b.data_ptr() + 4 * N] for b in bufs], [2 * N])      # the right half of a wider Y
+    torch.cuda.synchronize()
+    want = port.mul_mat(wb, 45, K, x)
+    for b in bufs:
+        got = b.cpu().numpy()
+        assert_bits(got[:, N:], want, "tcgen05 push")
+        assert (got[:, :N] == -1.0).all()
