@@ -64,3 +64,39 @@ def test_null_arguments_return_status_not_crash(lib):
     assert lib.rq_w4a4_mul_mat(None, 1, None, 0, 1, None, None, 1.0, 64, 0, None, 0, None) == -1
     assert lib.rq_w4a4_quantize(None, 4096, 1, 4096, 0, 1.0, 64, 0, None, 0, None) == -1
     assert lib.rq_w4a4_rotate(None, 4096, 1, 4096, 4096, None, 4096, None) == -1
+
+
+ENV_PROBE = r"""
+import ctypes, sys
+import ruquant_b200 as rq
+L = rq.lib()
+out = []
+for type_, header in [(44, 0.0), (44, 0.9), (45, 0.0), (45, 0.85)]:
+    d = rq.WeightDesc()
+    d.type, d.header_clip = type_, header
+    out.append("%.4f" % L.rq_w4a4_resolve_clip(ctypes.byref(d)))
+out.append(str(L.rq_w4a4_act_group()))
+print(" ".join(out))
+"""
+
+
+@pytest.mark.parametrize("env,want", [
+    ({}, "1.0000 0.9000 1.0000 0.8500 64"),                                    # unset: header clip, else 1; groups of 64
+    ({"RQ_ACT_CLIP": "0.7"}, "0.7000 0.7000 0.7000 0.7000 64"),                # one switch serves both types
+    ({"RQ_ACT_CLIP": "0.7", "RQ_ACT_CLIP_H": "0.6"}, "0.7000 0.7000 0.6000 0.6000 64"),
+    ({"RQ_ACT_CLIP_H": "0.6"}, "1.0000 0.9000 0.6000 0.6000 64"),
+    ({"RQ_ACT_CLIP": "0"}, "1.0000 0.9000 1.0000 0.8500 64"),                  # not positive: ignored
+    ({"RQ_ACT_GROUP": "128"}, "1.0000 0.9000 1.0000 0.8500 128"),
+    ({"RQ_ACT_GROUP": "256"}, "1.0000 0.9000 1.0000 0.8500 256"),
+    ({"RQ_ACT_GROUP": "100"}, "1.0000 0.9000 1.0000 0.8500 64"),               # anything else: 64
+])
+def test_environment_switches_resolve_as_in_the_reference(env, want):
+    """ggml_rq_act_clip_for and ggml_rq_act_group (patch:2590-2600, 2623-2631): read once per process, so each setting
+    gets its own interpreter."""
+    import subprocess
+    import sys
+    e = {k: v for k, v in os.environ.items() if not k.startswith("RQ_ACT_")}
+    e.update(env)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    got = subprocess.run([sys.executable, "-c", ENV_PROBE], env=e, cwd=root, capture_output=True, text=True, check=True).stdout.strip()
+    assert got == want

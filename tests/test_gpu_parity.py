@@ -418,3 +418,17 @@ def test_push_from_the_tcgen05_kernel(rq, port):
         got = b.cpu().numpy()
         assert_bits(got[:, N:], want, "tcgen05 push")
         assert (got[:, :N] == -1.0).all()
+
+
+def test_eight_rotation_blocks(rq, port):
+    """RQ_ROT_BLOCKS = 8 (the widest split the reference's converter documents): K = 8 x 2560 is rotated in blocks of
+    2560 = 20 x 128; weights from the GPU quantizer and from the oracle agree, and so do the products on every path."""
+    K, N = 8 * 2560, 48
+    wf = inputs.normal_weights(N, K, 9600)
+    wb = port.quantize_weights(wf, 45, rot_blocks=8)
+    got = rq.quantize_weights(dev(wf), 45, 0, 8)
+    torch.cuda.synchronize()
+    assert (got.cpu().numpy() == wb).all()
+    for M, path in [(1, 1), (5, 1), (70, 2)]:
+        x = inputs.outlier_activations(M, K, 9601 + M)
+        assert_bits(gpu_mul_mat(rq, wb, 45, K, x, path=path), port.mul_mat(wb, 45, K, x), "rot8 M=%d" % M)
