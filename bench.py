@@ -169,7 +169,6 @@ def run_ours(args):
     groups = []        # (K, x_dev, workspace, [(N_total, N_local, Weight, y_local, y_full)], gather or None)
     mats = []          # flat list of (K, N_total) for the byte count
     n_layer_local = sum(N // world for _n, _k, N in LAYER)
-    layer_bufs = []
     # all activations of a pass in one device arena, all layer outputs in another: the end-to-end step is then one
     # pinned-host -> device copy and one device -> host copy around the captured graph
     k_layer = sum(LAYER_DIMS[names[0]][0] for names in GROUPS)
@@ -238,7 +237,6 @@ def run_ours(args):
             y_layer_loc = y_layer_all[rank * n_layer_local:(rank + 1) * n_layer_local]
         else:
             y_layer_loc = torch.empty((n_layer_local,), device=dev, dtype=torch.float32)
-        layer_bufs.append(y_layer_loc)
         col = 0
         for gi, names in enumerate(GROUPS):
             K = LAYER_DIMS[names[0]][0]

@@ -224,7 +224,6 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                 int pa[SP][2][NT][4];
 #pragma unroll
                 for (int sp = 0; sp < SP; ++sp) {
-                    const int j = c * CH_STEPS + h + sp;          // 64-input step of the tile
                     const uint4 wv = sp_[(h + sp) * 32];
                     uint4 b[NT];
 #pragma unroll
