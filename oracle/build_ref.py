@@ -10,7 +10,7 @@ the command line), writes them verbatim, between a small prelude and a threaded 
 `oracle/_ref/ruquant_ref.c` (git-ignored), and compiles that one file with gcc the way ggml-base is compiled
 (-O3 -std=gnu11, no -march, so no FMA contraction).  No reference line is stored in this repository.
 
-Usage: python oracle/build_ref.py [/path/to/reference]   (default /root/reference)
+Usage: python oracle/build_ref.py [/path/to/reference]   (default: $RQ_REFERENCE_DIR, else REFERENCE_DIR below)
 """
 import os
 import subprocess
@@ -111,8 +111,11 @@ def _balanced(lines):
     return text.count("{") == text.count("}")
 
 
+REFERENCE_DIR = "/root/reference"
+
+
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RQ_REFERENCE_DIR", REFERENCE_DIR)
     patch = os.path.join(ref, "patches", "llama.cpp-ruquant.patch")
     if not os.path.exists(patch):
         print("reference not present (%s): nothing built" % patch)
