@@ -432,3 +432,21 @@ def test_eight_rotation_blocks(rq, port):
     for M, path in [(1, 1), (5, 1), (70, 2)]:
         x = inputs.outlier_activations(M, K, 9601 + M)
         assert_bits(gpu_mul_mat(rq, wb, 45, K, x, path=path), port.mul_mat(wb, 45, K, x), "rot8 M=%d" % M)
+
+
+@pytest.mark.parametrize("M", [129, 257, 300])
+def test_pairs_with_ragged_token_and_row_counts(rq, port, M):
+    """CTA pairs (above 128 tokens) when the last pair's second CTA holds one token, none, or a partial tile, the weight
+    rows do not fill their last 256-row tile, and y has a row stride that is not a multiple of 4 floats."""
+    K, N = 1024, 300
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9700), 45)
+    w = rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    x = inputs.outlier_activations(M, K, 9700 + M)
+    ybuf = torch.full((M, N + 3), -2.0, dtype=torch.float32, device="cuda")
+    ws = rq.new_workspace(K, M)
+    rq.mul_mat(w, dev(x), out=ybuf[:, :N], path=2, workspace=ws)
+    torch.cuda.synchronize()
+    rq.device_status(ws, K, M)
+    got = ybuf.cpu().numpy()
+    assert_bits(np.ascontiguousarray(got[:, :N]), port.mul_mat(wb, 45, K, x), "ragged pair M=%d" % M)
+    assert (got[:, N:] == -2.0).all()
