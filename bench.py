@@ -13,7 +13,9 @@ copies of its outputs inside the timed region.  `prefill` reports the M = 4096 g
 (K=5120, N=17408) in TOPS, whole node (rotate + quantize + tcgen05 GEMM + fold + epilogue).
 
 With N GPUs the weight rows are sharded along N, the activations are replicated and each layer's output (its seven
-matmul outputs side by side) is assembled with one NCCL all-gather (total work fixed: "strong" scaling).
+matmul outputs side by side) is assembled on every rank: by default the kernels' epilogues store into every rank's
+output buffer (mapped through symmetric memory) and one barrier kernel per layer closes the exchange; --gather nccl, or
+a failed set-up, uses one NCCL all-gather per layer instead (total work fixed: "strong" scaling).
 """
 import argparse
 import json
@@ -315,7 +317,9 @@ def run_ours(args):
         flag = torch.tensor([1 if same else 0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) != 1:
-            raise SystemExit("pushed outputs differ from the all-gathered ones (or a barrier timed out)")
+            push["check"] = "FAILED: pushed outputs differ from the all-gathered ones (or a barrier timed out)"
+            if rank == 0:
+                print(push["check"], file=sys.stderr)
     g_gemv = capture(lambda: enqueue_pass(False)) if world == 1 else None
 
     def barrier():
@@ -448,7 +452,9 @@ def run_ours(args):
                 flag = torch.tensor([1 if same else 0], device=dev)
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
                 if int(flag.item()) != 1:
-                    raise SystemExit("prefill: pushed output differs from the all-gathered one")
+                    push["check"] = "FAILED: prefill pushed output differs from the all-gathered one"
+                    if rank == 0:
+                        print(push["check"], file=sys.stderr)
             ms_gemm = timed(gemm_only, max(3, args.steps), 3)
             rq.device_status(ws, K, M)
             ops = 2.0 * M * N * K
@@ -481,7 +487,7 @@ def run_ours(args):
                            "l2": "inputs larger than L2 (weights streamed once per step)",
                            "parallelism": ("single GPU" if world == 1 else
                                            "N-sharded x%d, GEMV epilogues store into every rank's output over NVLink, one barrier kernel "
-                                           "per layer (checked against an NCCL all-gather)" % world if push is not None else
+                                           "per layer (check against an NCCL all-gather: %s)" % (world, push.get("check", "equal")) if push is not None else
                                            "N-sharded x%d, one NCCL all-gather per layer output" % world),
                            "cuda_graph": True},
                 "frac_of_hbm_peak": value / (hbm_peak * world), "peak_kind": "of " + peak_kind,
