@@ -611,7 +611,15 @@ def run_single(args):
             stream.synchronize()
         return e0.elapsed_time(e1) * 1e3 / args.steps / copies      # us per matmul
 
+    def nofold():
+        for w in weights:
+            rq.tc_nofold_probe(w, M, ws, y, stream=stream)
+
     us_node, us_con, us_q = timed(node), timed(contraction), timed(quant_only)
+    us_probe = None
+    if layouts & rq.PREPACK_PREFILL and (args.path == 2 or M > 64):
+        quant_only()                  # leave an activation of the right format in the workspace
+        us_probe = timed(nofold)
     rq.device_status(ws, K, M)
     hbm_peak, _, kind = measured_peaks()
     ab, ops = algorithmic_bytes(K, N, M), 2.0 * M * N * K
@@ -619,7 +627,9 @@ def run_single(args):
                       "us_node": us_node, "us_contraction": us_con, "us_rotate_quantize": us_q,
                       "GBps_node": ab / us_node / 1e3, "GBps_contraction": ab / us_con / 1e3,
                       "frac_hbm_node": ab / us_node / 1e3 / hbm_peak, "frac_hbm_contraction": ab / us_con / 1e3 / hbm_peak,
-                      "TOPS_node": ops / us_node / 1e6, "TOPS_contraction": ops / us_con / 1e6, "peak_kind": "of " + kind}))
+                      "TOPS_node": ops / us_node / 1e6, "TOPS_contraction": ops / us_con / 1e6,
+                      "us_nofold_probe": us_probe, "TOPS_nofold_probe": (ops / us_probe / 1e6) if us_probe else None,
+                      "peak_kind": "of " + kind}))
 
 
 def main():

@@ -111,8 +111,14 @@ size_t rq_w4a4_prepack_bytes(int type, int64_t K, int64_t N, int layouts);
 int rq_w4a4_prepare(const void * w_blocks_dev, int type, int64_t K, int64_t N, void * prepack_dev, size_t prepack_bytes,
                     int layouts, rq_weight_desc * out_desc, void * stream);
 
-/* Bytes of the per-call workspace (quantized activations and a status word) for M tokens of width K. */
+/* Bytes of the per-call workspace (quantized activations and a 256-byte status block) for M tokens of width K. */
 size_t rq_w4a4_workspace_bytes(int64_t K, int64_t M);
+
+/* Zeroes the workspace's status block (a memset node: capture-safe).  Call it once after allocating a workspace --
+ * or before each use when the memory comes from a pool, as ggml-cuda's does -- because the error word of the block is
+ * sticky: kernels only ever set it, so that a report survives later calls until rq_w4a4_device_status reads it.  A
+ * build with -DRQ_TRACE also reads a buffer address from the block; garbage there would be dereferenced. */
+int rq_w4a4_workspace_init(void * workspace_dev, int64_t K, int64_t M, void * stream);
 
 /* The MUL_MAT node.  Capture-safe: only enqueues on `stream`.  y[i][t*ldy[i] + n] for n_w (1..3) weights that
  * share the activation x (f32, row stride ldx floats, rows 16-byte aligned): rotate (W4A4H) -> quantize -> GEMV
@@ -156,8 +162,9 @@ int rq_w4a4_act_format(const rq_weight_desc * const * w, int n_w, int64_t M, int
 int rq_w4a4_workspace_layout(int64_t K, int64_t M, int act_group, uint64_t * off_a8, uint64_t * off_msh, uint64_t * off_u,
                              uint64_t * off_status);
 
-/* Synchronises `stream` and returns RQ_OK or RQ_ERR_DEVICE if a kernel of an earlier call on this workspace gave
- * up on a bounded wait.  Not capture-safe. */
+/* Synchronises `stream` and returns RQ_OK, RQ_ERR_DEVICE if a kernel of ANY earlier call on this workspace gave up on
+ * a bounded wait, or RQ_ERR_MISMATCH if a contraction kernel met an activation quantized in the other format.  The
+ * report is sticky until this call reads it (and clears it).  Not capture-safe. */
 int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream);
 
 /* N-sharded ranks of one node (the reference assembles the outputs with a collective after the node; here the node
@@ -169,7 +176,17 @@ int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * str
  * n_ranks words, peer-mapped, zero-initialised) and waits, bounded, until its own array shows that epoch from every
  * rank; the epoch counts up in *epoch_dev (local device memory, zero-initialised), so a captured graph replays
  * correctly.  On expiry of the wait *status_dev becomes 3 and the kernel returns.  One barrier kernel per GPU; ranks
- * are separate processes or threads, one per GPU. */
+ * are separate processes or threads, one per GPU.
+ * Rules the caller keeps:
+ *  - every rank calls the barrier the same number of times, in the same places: a rank whose epoch lags behind passes
+ *    without waiting (the comparison is "at least this epoch"), it does not wait for the others to catch up;
+ *  - a rank leaves barrier k as soon as all flags show epoch k, and may then push again while its peers still run
+ *    what they placed between barrier k and barrier k+1.  So a destination pushed to after barrier k must not alias
+ *    memory that any peer still reads before ITS barrier k+1: keep two copies of such an output and alternate
+ *    (double-buffering), or place a second barrier after the readers.  ggml reuses graph buffers, so an adapter that
+ *    pushes straight into dst tensors needs one of the two;
+ *  - all y_dst[d * n_w + i] of a call must be 4-byte aligned; 16-byte stores are used only when every destination
+ *    (and ldy) allows them. */
 int rq_w4a4_mul_mat_push(const rq_weight_desc * const * w, int n_w, const float * x_dev, int64_t ldx, int64_t M,
                          float * const * y_dst, int n_dst, const int64_t * ldy, float clip, int act_group,
                          void * workspace_dev, size_t workspace_bytes, void * stream);
@@ -195,6 +212,13 @@ int rq_w4a4_quantize_weights(const float * w_dev, int64_t ldw, int type, int64_t
  * should be made outside stream capture. */
 int rq_w4a4_mul_mat_static(const rq_weight_desc * w, const float * x_dev, int64_t ldx, int64_t M, float * y_dev, int64_t ldy,
                            float clip, int act_group, int path, void * stream);
+
+/* Measurement aid, not the MUL_MAT: the tcgen05 kernel run with the whole of K in one accumulator per output (no
+ * per-group hand-over out of tensor memory, no fold), on an activation already quantized into the workspace.  A
+ * benchmark times it next to rq_w4a4_mul_mat_quantized to see what the per-group fold of the reference's format costs
+ * on this kernel.  The values written to y_dev are meaningless. */
+int rq_w4a4_tc_nofold_probe(const rq_weight_desc * w, int64_t M, float * y_dev, int64_t ldy, void * workspace_dev,
+                            size_t workspace_bytes, void * stream);
 
 const char * rq_status_string(int status);
 int rq_last_cuda_error(void);   /* cudaError_t of the last failed runtime call on this thread */

@@ -23,6 +23,7 @@ EXPORTS = [
     "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
     "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n", "rq_w4a4_act_format",
     "rq_w4a4_quantize_weights", "rq_w4a4_quantize_weights_scratch_bytes", "rq_w4a4_mul_mat_push", "rq_rank_barrier",
+    "rq_w4a4_workspace_init", "rq_w4a4_tc_nofold_probe",
 ]
 
 
@@ -84,6 +85,8 @@ def lib():
         u64p = ctypes.POINTER(ctypes.c_uint64)
         L.rq_w4a4_workspace_layout.argtypes = [i64, i64, i32, u64p, u64p, u64p, u64p]
         L.rq_w4a4_device_status.argtypes = [vp, i64, i64, vp]
+        L.rq_w4a4_workspace_init.argtypes = [vp, i64, i64, vp]
+        L.rq_w4a4_tc_nofold_probe.argtypes = [pd, i64, vp, i64, vp, sz, vp]
         L.rq_status_string.argtypes = [i32]
         L.rq_status_string.restype = ctypes.c_char_p
         L.rq_last_cuda_error.argtypes = []
@@ -150,8 +153,12 @@ def workspace_bytes(K, M):
 
 
 def new_workspace(K, M, device="cuda"):
+    """A workspace for M tokens of width K with its status block zeroed (the error word in it is sticky)."""
     import torch
-    return torch.empty(workspace_bytes(K, M), dtype=torch.uint8, device=device)
+    ws = torch.empty(workspace_bytes(K, M), dtype=torch.uint8, device=device)
+    with torch.cuda.device(ws.device):
+        _check(lib().rq_w4a4_workspace_init(ws.data_ptr(), K, M, _stream_ptr()), "rq_w4a4_workspace_init")
+    return ws
 
 
 def workspace_views(ws, K, M, group):
@@ -322,6 +329,16 @@ def mul_mat_quantized(weight, M, workspace, out=None, act_group=64, path=PATH_AU
     return out
 
 
+def tc_nofold_probe(weight, M, workspace, out, stream=None):
+    """Measurement aid: the tcgen05 kernel with all of K in one accumulator (no per-group fold); `out` gets no MUL_MAT."""
+    import torch
+    with torch.cuda.device(workspace.device):
+        _check(lib().rq_w4a4_tc_nofold_probe(ctypes.byref(weight.desc), M, out.data_ptr(), out.stride(0), workspace.data_ptr(),
+                                             workspace.numel(), _stream_ptr(stream)), "rq_w4a4_tc_nofold_probe")
+    return out
+
+
 def device_status(workspace, K, M, stream=None):
-    """Synchronises and raises if a kernel of the last call on this workspace gave up on a bounded wait."""
+    """Synchronises and raises if a kernel of any earlier call on this workspace gave up on a bounded wait or met an
+    activation in the wrong format (the report is sticky until read)."""
     _check(lib().rq_w4a4_device_status(workspace.data_ptr(), K, M, _stream_ptr(stream)), "rq_w4a4_device_status")

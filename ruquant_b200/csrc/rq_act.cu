@@ -13,15 +13,16 @@
 //
 // Two kernels:
 //   rq_act_kernel<P>          one CTA per token, the token's row resident in shared memory (prefill widths, any G).
-//   rq_act_cluster_kernel<P>  a thread-block cluster per token for decode widths: the CTAs transform disjoint chunks,
-//                             exchange columns through distributed shared memory, split the Paley outputs between
-//                             them and agree on the token's range with one more cluster barrier.
+//   rq_act_cluster_kernel<P>  a thread-block cluster per token for decode widths: every CTA transforms the whole row
+//                             (redundant, but it spares a gather through distributed shared memory), the Paley outputs
+//                             are split between the CTAs, and one cluster barrier agrees on the token's range.
 // Both start their successor early (programmatic dependent launch) and build the sign table before they wait for
 // the kernel that produced x.
 #include <cooperative_groups.h>
 
 #include <stdlib.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "rq_common.cuh"
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
     for (int i = tid; i < K / 32; i += nt) asm volatile("prefetch.global.L2 [%0];" :: "l"(prm.x + (int64_t) t * prm.ldx + i * 32));
     if constexpr (P > 1) build_sign_table(table, chi, P, tid, nt);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (t == 0 && tid == 0 && prm.status != nullptr) { prm.status[0] = 0; prm.status[1] = prm.fmt; }
+    if (t == 0 && tid == 0 && prm.status != nullptr) prm.status[1] = prm.fmt;     // word 0 (errors) is sticky: only the host clears it
     RQ_STAMP(tid == 0);                                     // 1: after the wait
 
     const float * xrow = prm.x + (int64_t) t * prm.ldx;
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_cluster_kernel(const ActParams
     build_sign_table(table, chi, P, tid, nt);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     RQ_STAMP(tid == 0);                                     // 1: after the wait
-    if (t == 0 && rank == 0 && tid == 0 && prm.status != nullptr) { prm.status[0] = 0; prm.status[1] = prm.fmt; }
+    if (t == 0 && rank == 0 && tid == 0 && prm.status != nullptr) prm.status[1] = prm.fmt;
 
     // ---- Sylvester transform of every chunk of the row
     load_fwht(prm.x + (int64_t) t * prm.ldx, row, K, m, tid, nt);
@@ -282,7 +283,8 @@ cudaError_t launch_ex(Kern kern, dim3 grid, dim3 block, size_t smem, int cluster
     cudaLaunchAttribute attr[2];
     int na = 0;
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = getenv("RQ_NO_PDL") ? 0 : 1;
+    static const int pdl = getenv("RQ_NO_PDL") ? 0 : 1;      // read once
+    attr[na].val.programmaticStreamSerializationAllowed = pdl;
     ++na;
     if (cluster_x > 1) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
@@ -317,22 +319,28 @@ cudaError_t configure() {
 
 template <int P>
 cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
+    // first use on a device (normally rq_w4a4_prepare's); several host threads may get here at once
+    static std::mutex mu;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 64 && !configured[dev]) {
-        e = configure<P>();
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[dev]) {
+            e = configure<P>();
+            if (e != cudaSuccess) return e;
+            configured[dev] = true;
+        }
     }
     const int K = prm.K;
-    static const int min_p = getenv("RQ_TUNE_ACT_MINP") ? atoi(getenv("RQ_TUNE_ACT_MINP")) : 0;
+    static const int min_p = rq_env_int("RQ_TUNE_ACT_MINP", 0);
     if (P > 1 && P >= min_p && prm.a8 != nullptr && prm.rot_out == nullptr && prm.G == 64 && prm.m % 64 == 0 && M <= 32) {
         // decode widths: a cluster per token
         constexpr int CP = P > 1 ? P : 12, CT = cluster_threads(CP);
         const int units = (K / prm.n_rot) * (prm.m / 64) * (CP / 4);
-        static const int c_max = getenv("RQ_TUNE_ACT_CMAX") ? atoi(getenv("RQ_TUNE_ACT_CMAX")) : 8;
+        static const int c_max = rq_env_int("RQ_TUNE_ACT_CMAX", 8);
         int C = c_max;
         while (C > 1 && units < 2 * C) C >>= 1;
         const int units_max = (units + C - 1) / C;
@@ -344,7 +352,7 @@ cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
     const size_t smem = ((size_t) K + (P > 1 ? (size_t) P * P : 0)) * sizeof(float);
     if (smem > SMEM_LIMIT) return cudaErrorInvalidValue;
     // few tokens and a cheap Paley stage: one big CTA per token keeps every phase short
-    static const int wide = getenv("RQ_TUNE_ACT_WIDE") ? atoi(getenv("RQ_TUNE_ACT_WIDE")) : 1;
+    static const int wide = rq_env_int("RQ_TUNE_ACT_WIDE", 1);
     if (P <= 20 && M <= 64 && wide) return launch_ex(rq_act_kernel<(P <= 20 ? P : 1), 1024>, dim3((unsigned) M), dim3(1024), smem, 1, stream, prm);
     return launch_ex(rq_act_kernel<P, ACT_THREADS>, dim3((unsigned) M), dim3(ACT_THREADS), smem, 1, stream, prm);
 }

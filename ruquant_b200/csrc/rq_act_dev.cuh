@@ -1,5 +1,4 @@
-// Device-side building blocks of the activation path (rotation + quantizer), shared by the stand-alone kernels
-// (rq_act.cu) and by the decode GEMV, which runs them inside every CTA for cheap rotations (rq_gemv.cu).
+// Device-side building blocks of the activation path (rotation + quantizer) used by the kernels of rq_act.cu.
 // Bit-parity contract: see rq_act.cu.
 #pragma once
 
@@ -234,19 +233,6 @@ __device__ __forceinline__ void load_fwht(const float * __restrict__ src, float 
         else if (rem == 4) fwht_pass<4>(dst, len, ls, tid, nt);
         else fwht_pass<2>(dst, len, ls, tid, nt);
         rq_cta_sync(bar, nt);
-    }
-}
-
-// the chunks a cluster CTA owns (global chunk rank + s*C -> local slot s), one warp per run of 32*EPT values
-template <int EPT>
-__device__ __forceinline__ void cluster_chunks(const float * __restrict__ xrow, float * chunks, int rank, int C, int nloc, int m,
-                                               int tid, int nt) {
-    const int warp = tid >> 5, nwarps = nt >> 5, lane = tid & 31;
-    const int rpc = m / (32 * EPT);                          // runs per chunk (1 up to m = 1024)
-    for (int r = warp; r < nloc * rpc; r += nwarps) {
-        const int s = r / rpc, sr = r - s * rpc;
-        load_transform_runs<EPT>(xrow + (size_t) (rank + s * C) * m + (size_t) sr * 32 * EPT,
-                                 chunks + (size_t) s * m + (size_t) sr * 32 * EPT, 1, true, 0, 1, lane);
     }
 }
 

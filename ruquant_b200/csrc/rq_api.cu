@@ -65,29 +65,32 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_supported(int type
 
 // ggml_rq_act_clip_for, patch:2590-2600: RQ_ACT_CLIP (and RQ_ACT_CLIP_H for rotated inputs, defaulting to
 // RQ_ACT_CLIP) win over the tensor's own clip, which wins over 1
+// A header clip that is not > 0 counts as unset there, NaN included; +infinity is treated as unset here as well (the
+// reference would scale every range by infinity).
+struct rq_env_clips { float plain, hadamard; };
 extern "C" __attribute__((visibility("default"))) float rq_w4a4_resolve_clip(const rq_weight_desc * w) {
-    static float env[2] = { -2.0f, -2.0f };
-    if (env[0] == -2.0f) {
+    static const rq_env_clips env = []() {          // read once; -1: not set (thread-safe static initialisation)
         const char * e = getenv("RQ_ACT_CLIP");
         const char * eh = getenv("RQ_ACT_CLIP_H");
-        const float e0 = e ? (float) atof(e) : -1.0f;
-        env[1] = eh ? (float) atof(eh) : e0;
-        env[0] = e0;
-    }
+        rq_env_clips c;
+        c.plain = e ? (float) atof(e) : -1.0f;
+        c.hadamard = eh ? (float) atof(eh) : c.plain;
+        return c;
+    }();
     const bool had = w != nullptr && w->type == RQ_TYPE_W4A4H;
-    const float e = env[had ? 1 : 0];
+    const float e = had ? env.hadamard : env.plain;
     const float t = w != nullptr ? w->header_clip : 0.0f;
-    return e > 0.0f ? e : t > 0.0f ? t : 1.0f;
+    if (e > 0.0f && !isinf(e)) return e;
+    return (t > 0.0f && !isinf(t)) ? t : 1.0f;
 }
 
 // ggml_rq_act_group, patch:2623-2631
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_act_group(void) {
-    static int g = 0;
-    if (g == 0) {
+    static const int g = []() {
         const char * e = getenv("RQ_ACT_GROUP");
         const int v = e ? atoi(e) : 64;
-        g = (v == 128 || v == 256) ? v : 64;
-    }
+        return (v == 128 || v == 256) ? v : 64;
+    }();
     return g;
 }
 
@@ -139,8 +142,7 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_prepare(const void
     out->layouts = layouts;
     out->K = K;
     out->N = N;
-    memcpy(&out->header_clip, &hdr.pad[1], 4);
-    if (!(out->header_clip == out->header_clip) || isinf(out->header_clip)) return RQ_ERR_CLIP;
+    memcpy(&out->header_clip, &hdr.pad[1], 4);      // kept as read; rq_w4a4_resolve_clip decides whether it counts
     out->wg64 = (((uint32_t) hdr.sum) >> 29) == 3u ? 1 : 0;
     out->wk_mode = flag ? 1 : 0;
     out->had_p = 1;
@@ -335,6 +337,25 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized(
     return RQ_OK;
 }
 
+// Measurement aid: the tcgen05 kernel with the whole of K in ONE accumulator per output, i.e. without the per-group
+// hand-over from tensor memory and without the fold.  The numbers it writes are not the MUL_MAT (the reference's
+// per-group shift is skipped); a benchmark times it to see what the same kernel reaches when nothing leaves tensor
+// memory between the first and the last input.
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_tc_nofold_probe(const rq_weight_desc * w, int64_t M, float * y_dev, int64_t ldy,
+                                                                           void * workspace_dev, size_t workspace_bytes, void * stream) {
+    if (w == nullptr || y_dev == nullptr || w->prepack == nullptr || (w->layouts & RQ_PREPACK_PREFILL) == 0) return RQ_ERR_ARG;
+    if (M < 1 || ldy < w->N) return RQ_ERR_SHAPE;
+    const rq_ws_layout l = rq_ws(w->K, M);
+    if (workspace_dev == nullptr || workspace_bytes < l.bytes) return RQ_ERR_WORKSPACE;
+    const uint8_t * ws = static_cast<const uint8_t *>(workspace_dev);
+    const uint8_t * pp = static_cast<const uint8_t *>(w->prepack);
+    RQ_CUDA(rq_launch_gemm_tc(w->tmap_w8, reinterpret_cast<const float *>(pp + w->off_sw), w->wk_mode ? RQ_FMT_I8 : RQ_FMT_E4M3, w->K, w->N,
+                              reinterpret_cast<const int8_t *>(ws + l.off_a8), reinterpret_cast<const int32_t *>(ws + l.off_msh),
+                              reinterpret_cast<const float *>(ws + l.off_u), M, (int) w->K, y_dev, ldy,
+                              reinterpret_cast<int32_t *>(const_cast<uint8_t *>(ws) + l.off_status), (cudaStream_t) stream));
+    return RQ_OK;
+}
+
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_quantized_n(const rq_weight_desc * const * w, int n_w, int64_t M,
                                            float * const * y_dev, const int64_t * ldy, int act_group, int path,
                                            void * workspace_dev, size_t workspace_bytes, void * stream) {
@@ -453,14 +474,23 @@ extern "C" __attribute__((visibility("default"))) int rq_rank_barrier(uint32_t *
     return RQ_OK;
 }
 
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_workspace_init(void * workspace_dev, int64_t K, int64_t M, void * stream) {
+    if (workspace_dev == nullptr) return RQ_ERR_ARG;
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || M < 1) return RQ_ERR_SHAPE;
+    RQ_CUDA(cudaMemsetAsync(static_cast<uint8_t *>(workspace_dev) + rq_ws(K, M).off_status, 0, 256, (cudaStream_t) stream));
+    return RQ_OK;
+}
+
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * stream) {
     if (workspace_dev == nullptr) return RQ_ERR_ARG;
     if (K <= 0 || K % RQ_BLOCK_CODES != 0 || M < 1) return RQ_ERR_SHAPE;
     const rq_ws_layout l = rq_ws(K, M);
     int32_t st = 0;
-    RQ_CUDA(cudaMemcpyAsync(&st, static_cast<uint8_t *>(workspace_dev) + l.off_status, 4, cudaMemcpyDeviceToHost,
-                            (cudaStream_t) stream));
+    uint8_t * word = static_cast<uint8_t *>(workspace_dev) + l.off_status;
+    RQ_CUDA(cudaMemcpyAsync(&st, word, 4, cudaMemcpyDeviceToHost, (cudaStream_t) stream));
     RQ_CUDA(cudaStreamSynchronize((cudaStream_t) stream));
+    // the word is sticky (no kernel clears it): reading a report takes it away
+    if (st != 0) RQ_CUDA(cudaMemsetAsync(word, 0, 4, (cudaStream_t) stream));
     // 1: a bounded wait expired; 2: the activation was quantized in the other kernel's format
     return st == 0 ? RQ_OK : st == 2 ? RQ_ERR_MISMATCH : RQ_ERR_DEVICE;
 }

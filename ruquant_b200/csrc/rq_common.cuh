@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/rq_b200.h"
 
@@ -117,6 +118,12 @@ __device__ __forceinline__ void rq_trace_value(const int32_t * status, unsigned 
 #define RQ_STAMP(cond) ((void) 0)
 #define RQ_STAMP_FLUSH(cond, status, tag) ((void) 0)
 #endif
+
+// an integer tuning knob from the environment (call sites cache the result in a function-local static: read once)
+static inline int rq_env_int(const char * name, int fallback) {
+    const char * v = getenv(name);
+    return v != nullptr ? atoi(v) : fallback;
+}
 
 // Launchers (one per .cu file).  All enqueue on `stream` and return a cudaError_t.
 cudaError_t rq_launch_act(const float * x, int64_t ldx, int64_t M, int64_t K, int n_rot, int p, int m, float rot_scale,

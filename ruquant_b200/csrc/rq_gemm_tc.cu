@@ -1,29 +1,35 @@
-// Prefill-width contraction on the sm_100a tensor cores: tcgen05.mma kind::i8 with the accumulator in tensor memory,
-// operands staged by TMA, and the reference's per-group integer fold done by the epilogue warps straight out of
-// tensor memory while the tensor pipe works on the next group.
+// Prefill-width contraction on the sm_100a tensor cores: tcgen05.mma with the accumulator in tensor memory, operands
+// staged by TMA, and the reference's per-group fold done by the epilogue warps straight out of tensor memory while the
+// tensor pipe works on the next group.
 //
 // Why the accumulator leaves tensor memory every G inputs: the reference shifts each group's term right by 4 before
 // the int32 sum (ggml_vec_dot_w4a4_a4, ggml/src/ggml-cpu/quants.c in patches/llama.cpp-ruquant.patch:173), which is
-// not linear, so groups cannot be accumulated together.  Operand scaling makes that fold one instruction:
-//   A = activations, int8 8*(q - z_g), [M][K] K-major      (tokens are the MMA's M = 128 rows = TMEM lanes)
-//   B = weights,     int8 16*c,        [N][K] K-major      (weight rows are the MMA's N = 256 = TMEM columns)
-//   D = 128 * S_g after G/32 instructions of K = 32;   total += (m_g * D) >> 11   ( = (m_g*S_g) >> 4, exact)
-// An epilogue thread owns one token (one TMEM lane), so m_g is a single register per group.  Weights with
-// multipliers k != 1 are stored as k*c instead and folded as (D * m_g) >> 7.
+// not linear, so groups cannot be accumulated together.  Two operand formats:
+//   F8  (weights without multipliers, the usual case): A = e4m3 byte of (q - z_g) [M][K], B = e4m3 byte of c [N][K],
+//       tcgen05.mma kind::f8f6f4 with fp32 accumulators, which hold S_g exactly (sums of products of small integers);
+//       the fold (m_g * S_g) >> 4 is ONE round-down FMA per output on a running total kept in [2^23, 2^24).
+//   I8  (weights with multipliers k): A = int8 8*(q - z_g), B = int8 k*c, kind::i8, D = 8*k*S_g, term = (D * m_g) >> 7.
+// Tokens are the MMA's M rows (TMEM lanes), weight rows its N columns: an epilogue thread owns one token, so m_g is
+// one register per group.
 //
 // CTA = 128 tokens x 256 weight rows.  Warp 0 lane 0: TMA producer over a ring of 128-input K slices (128B swizzle).
-// Warp 1: TMEM allocation, lane 0 issues the MMAs into two 256-column accumulator buffers.  Warps 4-11: fold + final
-// fp32 epilogue y = ((float(total) * 16) * u) * s_w.
-// The kernel is bound by the L2 -> shared-memory feed of its operands, so above 128 tokens two CTAs work as a pair
-// (PAIR, a cluster of 2, tcgen05 cta_group::2): one MMA of M = 256 spans both CTAs' tensor memory, each CTA stages
-// its own 128 tokens of A and only HALF of the 256 weight rows of B (32 KB per slice instead of 48 KB, six stages).
-// The even CTA issues the MMAs for both; its commits signal the barriers of both CTAs, the odd CTA's TMA bytes and
-// epilogue arrivals are counted on the even CTA's barriers.
+// Warp 1: TMEM allocation and MMA issue into two 256-column accumulator buffers.  Warps 4-11: fold + final fp32
+// epilogue y = ((float(total) * 16) * u) * s_w.  What bounds the kernel is the epilogue warps: per 64 inputs the two
+// MMAs take 256 cycles, 32 K accumulators cross from tensor memory to registers (128 KB) and are folded by 32 K FMAs
+// (256 cycles of the fp32 pipe), so the fold loop is written for issue slots: packed two-wide FMAs, the first
+// tensor-memory load of a group issued before the last piece of the previous group is folded, multipliers fetched four
+// groups at a time.
+// Above 128 tokens two CTAs work as a pair (PAIR, a cluster of 2, tcgen05 cta_group::2): one MMA of M = 256 spans both
+// CTAs' tensor memory, each CTA stages its own 128 tokens of A and only HALF of the 256 weight rows of B (32 KB per
+// slice instead of 48 KB, six stages).  The even CTA issues the MMAs for both; its commits signal the barriers of both
+// CTAs, the odd CTA's TMA bytes and epilogue arrivals are counted on the even CTA's barriers.
 // Every wait is bounded: on expiry the waiter raises a CTA-wide abort flag and a status word in global memory,
 // everyone leaves the pipeline, outstanding TMA transactions are drained and tensor memory is released.
 #include <cuda.h>
 
 #include <stdlib.h>
+
+#include <mutex>
 
 #include "rq_common.cuh"
 
@@ -101,14 +107,15 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
 }
 // instruction descriptor, kind::i8: D = s32 (2 at [4,6)), A and B signed int8 (1 at [7,10) and [10,13)), both
 // K-major (0 at 15, 16), N >> 3 at [17,23), M >> 4 at [24,29)
-constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
+constexpr int BNI = BN / 2;     // weight rows per MMA instruction: a tile's 256 rows go through two instructions with accumulators of their own
+constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
 // kind::f8f6f4: D = f32 (1 at [4,6)), A and B e4m3 (0 at [7,10) and [10,13)), K-major, same N and M fields
-constexpr uint32_t IDESC_F8 = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
+constexpr uint32_t IDESC_F8 = (1u << 4) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
 // a pair's instruction covers M = 256 tokens, 128 in each CTA's tensor memory
-constexpr uint32_t IDESC_PAIR = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) ((2 * BM) >> 4) << 24);
-constexpr uint32_t IDESC_F8_PAIR = (1u << 4) | ((uint32_t) (BN >> 3) << 17) | ((uint32_t) ((2 * BM) >> 4) << 24);
+constexpr uint32_t IDESC_PAIR = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) ((2 * BM) >> 4) << 24);
+constexpr uint32_t IDESC_F8_PAIR = (1u << 4) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) ((2 * BM) >> 4) << 24);
 
-// One instruction of K = 32 (128 tokens x 256 weight rows, or 256 x 256 for a pair).  ACC selects between starting and
+// One instruction of K = 32 (128 tokens x 128 weight rows, or 256 x 128 for a pair).  ACC selects between starting and
 // continuing an accumulator as two separate instructions with constant predicates: the issuing thread is the
 // bottleneck of this kernel the moment it spends more than an instruction's 128 cycles between two issues, so nothing
 // is computed per instruction that a template can decide.
@@ -162,42 +169,82 @@ __device__ __forceinline__ void tmem_ld_wait(int (&v)[32]) {
                  :: "memory");
 }
 
-// one integer multiply and one shift-add per output per group (measured on B200: 50+ outputs per clock per SM,
-// against 30 for a high multiply-add)
-// integer path (weights k*c, activations 8*(q - z)): D = 8*k*S, term = (D * m) >> 7
-__device__ __forceinline__ void fold32(int (&tot)[128], int base, const int (&v)[32], int mm) {
+// integer path (weights k*c, activations 8*(q - z)): D = 8*k*S, term = (D * m) >> 7: one integer multiply and one
+// shift-add per output per group (measured on B200: 50+ outputs per clock per SM, against 30 for a high multiply-add)
+template <int BASE>
+__device__ __forceinline__ void fold32_i8(int (&tot)[128], const int (&v)[32], int mm) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) tot[base + i] += (v[i] * mm) >> 7;
+    for (int i = 0; i < 32; ++i) tot[BASE + i] += (v[i] * mm) >> 7;
 }
 
 // fp8 path: D = S exactly (fp32 accumulation of products of small integers).  The running total lives in a float
 // kept inside [2^23, 2^24), where the spacing of floats is 1: a round-down fused multiply-add
 //     t <- fma.rm(S, m/16, t)
 // adds floor(S*m/16) = (m*S) >> 4 exactly (S*m/16 has at most 21 + 4 significant bits below 2^23, the sum is rounded
-// once, downwards, to an integer) -- the reference's shifted term in ONE instruction at the full fp32 rate.
-constexpr float FOLD_MAGIC = 12582912.0f;        // 1.5 * 2^23
-constexpr int FOLD_MAGIC_BITS = 0x4B400000;
-__device__ __forceinline__ float fma_rm(float a, float b, float c) {
-    float d;
-    asm("fma.rm.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
+// once, downwards, to an integer) -- the reference's shifted term in ONE instruction.  Two neighbouring columns share
+// a 64-bit register pair and one packed instruction (fma.rm.f32x2): half the issue slots of the scalar form.
+constexpr int FOLD_MAGIC_BITS = 0x4B400000;      // 1.5 * 2^23
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, uint32_t & lo, uint32_t & hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
 }
 template <int BASE>
-__device__ __forceinline__ void fold32_f8(float (&tf)[128], const int (&v)[32], float mf) {
+__device__ __forceinline__ void fold32_f8(uint64_t (&tf)[64], const int (&v)[32], uint64_t mf2) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) tf[BASE + i] = fma_rm(__int_as_float(v[i]), mf, tf[BASE + i]);
+    for (int i = 0; i < 16; ++i) {
+#ifdef RQ_TC_SCALAR_FMA
+        uint32_t lo, hi, m0, m1;
+        unpack2(tf[BASE / 2 + i], lo, hi);
+        unpack2(mf2, m0, m1);
+        float a, b;
+        asm("fma.rm.f32 %0, %1, %2, %3;" : "=f"(a) : "f"(__int_as_float(v[2 * i])), "f"(__uint_as_float(m0)), "f"(__uint_as_float(lo)));
+        asm("fma.rm.f32 %0, %1, %2, %3;" : "=f"(b) : "f"(__int_as_float(v[2 * i + 1])), "f"(__uint_as_float(m1)), "f"(__uint_as_float(hi)));
+        tf[BASE / 2 + i] = pack2(__float_as_uint(a), __float_as_uint(b));
+#else
+        asm("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(tf[BASE / 2 + i]) : "l"(pack2((uint32_t) v[2 * i], (uint32_t) v[2 * i + 1])), "l"(mf2));
+#endif
+    }
 }
-// Every 1536 inputs the float is re-centred: what it holds above +-2^19 moves, in units of 2^20, into a signed byte
-// of a packed carry word, so the float never leaves its window.  Bounds: a group of G inputs adds at most
-// 255 * (G*15*8) / 16 in magnitude, 2.94 M per 1536 inputs, on top of at most 2^19 left by the last re-centring:
-// |t - magic| < 3.5 M < 2^22; a re-centring moves at most 4 units, K <= 32768 has at most 22 of them: |byte| <= 88.
-__device__ __forceinline__ void recenter(float (&tf)[128], int (&carry)[32]) {
+// Re-centring.  A float in the window is 2^23 + mantissa with mantissa = 2^22 + t, t the running total since the last
+// re-centring; bits 20..22 of the mantissa are floor((t + 2^22) / 2^20), a digit in 0..7 that reads 4 for t in
+// [0, 2^20).  Every RECENTER_INPUTS inputs that digit moves into an unsigned byte of a packed carry word and is set
+// back to 4: three instructions per output.  Bounds: a group of G inputs adds at most 255 * (G*8*15) / 16 in magnitude,
+// 2.94 M per 1536 inputs, on top of t in [0, 2^20): the float stays inside [2^23 + 2^22 - 2.94 M, 2^23 + 2^22 + 2^20 +
+// 2.94 M), within the window; K <= 32768 has at most 32 re-centrings (groups of 256 re-centre every 1024 inputs, the
+// nearest multiple of four groups), so a byte holds at most 32 * 7 = 224.  At the end
+//     total = (sum of digits - 4 * number of re-centrings) * 2^20 + (mantissa & (2^20 - 1)).
+constexpr int RECENTER_INPUTS = 1536;
+// The carry words live in shared memory between re-centrings (the per-warp tile that later stages the transposed
+// store; word w of lane l at w * 32 + l: conflict-free) -- the registers they would take are the difference between a
+// fold loop that fits and one that spills.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+// Integer instructions run at half the rate of the FMAs on this part, so the re-centring counts them: byte 2 of each
+// of four floats (mantissa bits 16..23) is gathered with three byte permutes, one shift and one mask turn the four
+// bytes into the four digits, already packed as the carry word wants them; one logic op per float resets the digit.
+__device__ __forceinline__ void recenter(uint64_t (&tf)[64], uint32_t * carry_smem) {
+    const uint32_t base = smem_u32(carry_smem);
 #pragma unroll
-    for (int i = 0; i < 128; ++i) {
-        const int k = __float_as_int(tf[i]) - FOLD_MAGIC_BITS;
-        const int c = (k + (1 << 19)) >> 20;
-        tf[i] = __int_as_float(FOLD_MAGIC_BITS + (k - (c << 20)));
-        carry[i >> 2] += c << (8 * (i & 3));
+    for (int i = 0; i < 32; ++i) {          // carry word i: columns 4i .. 4i+3 = pairs 2i, 2i+1
+        uint32_t w[4];
+        unpack2(tf[2 * i], w[0], w[1]);
+        unpack2(tf[2 * i + 1], w[2], w[3]);
+        const uint32_t g = prmt(prmt(w[0], w[1], 0x0062u), prmt(w[2], w[3], 0x0062u), 0x5410u);
+        const uint32_t cw = (g >> 4) & 0x07070707u;
+        // a reduction without a return value: nothing waits for shared memory here (a load-add-store chain per word
+        // would, the fold leaves no registers to batch the loads)
+        asm volatile("red.shared.add.u32 [%0], %1;" :: "r"(base + (uint32_t) (i * 128)), "r"(cw) : "memory");
+#pragma unroll
+        for (int h = 0; h < 4; ++h) w[h] = (w[h] & 0xFF8FFFFFu) | 0x00400000u;
+        tf[2 * i] = pack2(w[0], w[1]);
+        tf[2 * i + 1] = pack2(w[2], w[3]);
     }
 }
 
@@ -211,10 +258,12 @@ struct TcParams {
     int32_t * status;
     int K, N, M, G;
     int n_more;
+    int vec;                            // 16-byte stores are safe: ldy % 4 == 0 and every destination 16-byte aligned
 };
 
 struct __align__(8) TcShared {
-    uint64_t full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2];
+    uint64_t full[MAX_STAGES], empty[MAX_STAGES];
+    uint64_t tmem_full[4], tmem_empty[4];       // [accumulator buffer 0/1][half of the tile's weight rows 0/1]
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -248,8 +297,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sh.full[s]), 1); mbar_init(smem_u32(&sh.empty[s]), 1); }
-        // a pair's accumulator buffer is free when the 8 epilogue warps of BOTH CTAs have arrived (on rank 0's barrier)
-        for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&sh.tmem_full[b]), 1); mbar_init(smem_u32(&sh.tmem_empty[b]), PAIR ? 16 : 8); }
+        // half an accumulator buffer is free when its 4 epilogue warps (of BOTH CTAs of a pair, on rank 0's barrier) have arrived
+        for (int b = 0; b < 4; ++b) { mbar_init(smem_u32(&sh.tmem_full[b]), 1); mbar_init(smem_u32(&sh.tmem_empty[b]), PAIR ? 8 : 4); }
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -325,11 +374,12 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     } else if (warp == 1) {
         if (leader) {
             // The whole warp walks the loop with warp-uniform values (descriptors and addresses then live in the uniform
-            // datapath) and elects a lane at each MMA and commit.  Straight-line issue loop: shifts instead of divisions (gsteps is 1, 2 or 4), slot, phase and accumulator
+            // datapath) and elects a lane at each MMA and commit.  Straight-line issue loop: shifts instead of divisions (any number of 64-input steps per accumulator), slot, phase and accumulator
             // buffer as running counters, descriptors advanced by adding to their address field.
-            const uint32_t gmask = (uint32_t) gsteps - 1u;
             const uint64_t da0 = umma_desc(ring), db0 = umma_desc(ring + A_BYTES);
             uint32_t s = 0, ph = 0, gcount = 0;       // ring slot, its phase, accumulator groups issued (all units)
+            uint32_t gs = 0;                          // 64-input step inside the current group
+            const uint32_t gsteps_u = (uint32_t) gsteps;
             bool ok = true;
             RQ_CYC_DECL(c_full);
             RQ_CYC_DECL(c_tmem);
@@ -347,30 +397,40 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     const uint64_t da = da0 + so, db = db0 + so;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        const uint32_t gs = (2u * (uint32_t) ks + (uint32_t) h) & gmask;   // 64-input step inside its group
                         const uint32_t buf = gcount & 1u;
-                        const uint32_t d = tmem_base + buf * BN;
-                        if (gs == 0) {
-                            RQ_CYC_BEGIN(c_tmem);
-                            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_empty[buf]), ((gcount >> 1) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
-                            RQ_CYC_END(c_tmem);
-                            tc_fence_after();
-                            RQ_CYC_BEGIN(c_issue);
-                            umma<F8, PAIR, false>(d, da + h * 4, db + h * 4);          // bytes >> 4 inside the swizzled row
-                        } else {
-                            RQ_CYC_BEGIN(c_issue);
-                            umma<F8, PAIR, true>(d, da + h * 4, db + h * 4);
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            // The tile's 256 weight rows are two instructions of 128 with accumulators, barriers and epilogue
+                            // warps of their own: the first half is handed over while the second is still being multiplied.
+                            // A pair's instruction takes 64 rows from each CTA: its halves are rows {0-63, 128-191} and
+                            // {64-127, 192-255} of the tile.
+                            const uint32_t q = buf * 2u + (uint32_t) hf;
+                            const uint32_t d = tmem_base + q * BNI;
+                            const uint64_t dbh = db + (uint64_t) (hf * ((PAIR ? BH_BYTES / 2 : BH_BYTES) >> 4));
+                            if (gs == 0) {
+                                RQ_CYC_BEGIN(c_tmem);
+                                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_empty[q]), ((gcount >> 1) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
+                                RQ_CYC_END(c_tmem);
+                                tc_fence_after();
+                                RQ_CYC_BEGIN(c_issue);
+                                umma<F8, PAIR, false>(d, da + h * 4, dbh + h * 4);          // bytes >> 4 inside the swizzled row
+                            } else {
+                                RQ_CYC_BEGIN(c_issue);
+                                umma<F8, PAIR, true>(d, da + h * 4, dbh + h * 4);
+                            }
+                            umma<F8, PAIR, true>(d, da + h * 4 + 2, dbh + h * 4 + 2);
+                            RQ_CYC_END(c_issue);
+                            if (gs + 1u == gsteps_u) {
+                                RQ_CYC_BEGIN(c_commit);
+                                if (PAIR) umma_commit_pair(smem_u32(&sh.tmem_full[q]));
+                                else      umma_commit(smem_u32(&sh.tmem_full[q]));
+                                RQ_CYC_END(c_commit);
+                            }
                         }
-                        umma<F8, PAIR, true>(d, da + h * 4 + 2, db + h * 4 + 2);
-                        RQ_CYC_END(c_issue);
-                        if (gs == gmask) {
-                            RQ_CYC_BEGIN(c_commit);
-                            if (PAIR) umma_commit_pair(smem_u32(&sh.tmem_full[buf]));
-                            else      umma_commit(smem_u32(&sh.tmem_full[buf]));
-                            RQ_CYC_END(c_commit);
-                            ++gcount;
-                        }
+                        if (!ok) break;
+                        if (++gs == gsteps_u) { gs = 0; ++gcount; }
                     }
+                    if (!ok) break;
                     RQ_CYC_BEGIN(c_commit);
                     if (PAIR) umma_commit_pair(smem_u32(&sh.empty[s]));
                     else      umma_commit(smem_u32(&sh.empty[s]));
@@ -394,13 +454,23 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t lane_base = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (half * 128);
         // the quantizer records the format it wrote: refuse to multiply the wrong one
         const bool fmt_ok = prm.status == nullptr || prm.status[1] == (F8 ? RQ_FMT_E4M3 : RQ_FMT_I8);
-        const uint32_t empty_bar0 = PAIR ? map_to_cta(smem_u32(&sh.tmem_empty[0]), 0) : smem_u32(&sh.tmem_empty[0]);
-        const int recenter_every = 1536 / prm.G;           // G is 64, 128 or 256
-        const bool vec = ((prm.ldy & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.y) & 15) == 0);
+        // this half's barriers: index buffer * 2 + half
+        const uint32_t empty_bar0 = (PAIR ? map_to_cta(smem_u32(&sh.tmem_empty[0]), 0) : smem_u32(&sh.tmem_empty[0])) + (uint32_t) half * 8u;
+        const uint32_t full_bar0 = smem_u32(&sh.tmem_full[0]) + (uint32_t) half * 8u;
+        // groups between two re-centrings of the float totals: a multiple of four (the loop below walks four groups at a time)
+        const int recenter_every = prm.G >= 256 ? 4 : RECENTER_INPUTS / prm.G;
+        const bool vec = prm.vec != 0;
+        const bool m_vec = (n_ag & 3) == 0;            // a token's multipliers start on a 16-byte boundary
+        float * stg = reinterpret_cast<float *>(smem_raw + (ring - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) + e * 1024;
+        uint32_t * carry_smem = reinterpret_cast<uint32_t *>(stg) + lane;
         uint32_t gcount = 0;              // accumulator groups folded (all units)
         bool ok = true;
         RQ_CYC_DECL(c_tfull);
         RQ_CYC_DECL(c_epi);
+        RQ_CYC_DECL(c_hold);
+        RQ_CYC_DECL(c_rec);
+        RQ_CYC_DECL(c_fin);
+        RQ_CYC_DECL(c_tail);
         RQ_CYC_BEGIN(c_epi);
         for (int v = first; v < units && ok; v += stride) {
             const int n_tile = v / m_units, m_unit = v - n_tile * m_units;
@@ -408,73 +478,91 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int row = m_tile * BM + quarter * 32 + lane;
             const bool row_ok = row < prm.M;
             const int32_t * mrow = prm.msh + (size_t) (row_ok ? row : 0) * n_ag;
+            // the multipliers of four groups at a time (one 16-byte load where a token's row of them is aligned); rows
+            // beyond M fold with 0
+            auto load_m4 = [&](int ag) -> int4 {
+                int4 r = make_int4(0, 0, 0, 0);
+                if (!row_ok) return r;
+                if (m_vec) return __ldg(reinterpret_cast<const int4 *>(mrow + ag));
+                r.x = __ldg(mrow + ag);
+                if (ag + 1 < n_ag) r.y = __ldg(mrow + ag + 1);
+                if (ag + 2 < n_ag) r.z = __ldg(mrow + ag + 2);
+                if (ag + 3 < n_ag) r.w = __ldg(mrow + ag + 3);
+                return r;
+            };
             int tot[F8 ? 1 : 128];
-            float tf[F8 ? 128 : 1];
-            int carry[F8 ? 32 : 1];
+            uint64_t tf[F8 ? 64 : 1];
             if (F8) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i) tf[F8 ? i : 0] = FOLD_MAGIC;
+                for (int i = 0; i < 64; ++i) tf[F8 ? i : 0] = pack2((uint32_t) FOLD_MAGIC_BITS, (uint32_t) FOLD_MAGIC_BITS);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) carry[F8 ? i : 0] = 0;
+                for (int i = 0; i < 32; ++i) carry_smem[i * 32] = 0u;      // (the previous unit's store ended with a warp barrier)
             } else {
 #pragma unroll
                 for (int i = 0; i < 128; ++i) tot[F8 ? 0 : i] = 0;
             }
-            int since = 0;
-            int mnext = row_ok ? __ldg(mrow) : 0;
-            for (int ag = 0; ag < n_ag; ++ag, ++gcount) {
-                const uint32_t buf = gcount & 1u;
-                const int mm = mnext;
-                if (ag + 1 < n_ag) mnext = row_ok ? __ldg(mrow + ag + 1) : 0;
-                // the loads below are warp-collective: leave the loop together or not at all
-                RQ_CYC_BEGIN(c_tfull);
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_full[buf]), (gcount >> 1) & 1u, abort_flag))) { ok = false; break; }
-                RQ_CYC_END(c_tfull);
-                tc_fence_after();
-                const uint32_t t0 = lane_base + buf * BN;
-                if constexpr (F8) {
-                    const float mf = __int_as_float(mm);          // m / 16
-                    // four 32-column pieces, the load of piece c+1 in flight while piece c folds
-                    int va[32], vb[32];
-                    tmem_ld32(t0, va);
-                    tmem_ld_wait(va); tmem_ld32(t0 + 32, vb); fold32_f8<0>(tf, va, mf);
-                    tmem_ld_wait(vb); tmem_ld32(t0 + 64, va); fold32_f8<32>(tf, vb, mf);
-                    tmem_ld_wait(va); tmem_ld32(t0 + 96, vb); fold32_f8<64>(tf, va, mf);
-                    tmem_ld_wait(vb);
-                    // the accumulator is in registers: hand the buffer back before the last piece is folded
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
-                        else      mbar_arrive(empty_bar0 + buf * 8u);
+            int since = 0, n_rec = 0;
+            int4 mcur = load_m4(0);
+            // Software pipeline over 32-column pieces of the accumulator: the tensor-memory load of piece c+1 is in flight
+            // while piece c folds, and the first piece of the NEXT group is requested (its barrier permitting) before the
+            // last piece of this group folds, so a warp never sits out a whole load latency.
+            int va[32], vb[32];
+            RQ_CYC_BEGIN(c_tfull);
+            if (!__all_sync(0xffffffffu, mbar_wait(full_bar0 + (gcount & 1u) * 16u, (gcount >> 1) & 1u, abort_flag))) { ok = false; break; }
+            RQ_CYC_END(c_tfull);
+            tc_fence_after();
+            tmem_ld32(lane_base + (gcount & 1u) * BN, va);
+            for (int ag = 0; ag < n_ag && ok; ag += 4) {
+                const int mq[4] = { mcur.x, mcur.y, mcur.z, mcur.w };
+                if (ag + 4 < n_ag) mcur = load_m4(ag + 4);
+                const int cnt = n_ag - ag < 4 ? n_ag - ag : 4;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (j < cnt && ok) {
+                        const uint32_t buf = gcount & 1u;
+                        const uint32_t t0 = lane_base + buf * BN;
+                        uint64_t mf2 = 0;
+                        if constexpr (F8) mf2 = pack2((uint32_t) mq[j], (uint32_t) mq[j]);      // f32 bits of m / 16, twice
+                        const int mm = mq[j];
+                        RQ_CYC_BEGIN(c_hold);
+                        tmem_ld_wait(va); tmem_ld32(t0 + 32, vb);
+                        if constexpr (F8) fold32_f8<0>(tf, va, mf2); else fold32_i8<0>(tot, va, mm);
+                        tmem_ld_wait(vb); tmem_ld32(t0 + 64, va);
+                        if constexpr (F8) fold32_f8<32>(tf, vb, mf2); else fold32_i8<32>(tot, vb, mm);
+                        tmem_ld_wait(va); tmem_ld32(t0 + 96, vb);
+                        if constexpr (F8) fold32_f8<64>(tf, va, mf2); else fold32_i8<64>(tot, va, mm);
+                        tmem_ld_wait(vb);
+                        // the accumulator is in registers: hand the buffer back before the last piece is folded
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 16u);
+                            else      mbar_arrive(empty_bar0 + buf * 16u);
+                        }
+                        RQ_CYC_END(c_hold);
+                        RQ_CYC_BEGIN(c_tail);
+                        ++gcount;
+                        if (ag + j + 1 < n_ag) {
+                            // the loads are warp-collective: leave the loop together or not at all
+                            RQ_CYC_BEGIN(c_tfull);
+                            ok = __all_sync(0xffffffffu, mbar_wait(full_bar0 + (gcount & 1u) * 16u, (gcount >> 1) & 1u, abort_flag));
+                            RQ_CYC_END(c_tfull);
+                            if (ok) {
+                                tc_fence_after();
+                                tmem_ld32(lane_base + (gcount & 1u) * BN, va);
+                            }
+                        }
+                        if constexpr (F8) fold32_f8<96>(tf, vb, mf2); else fold32_i8<96>(tot, vb, mm);
+                        RQ_CYC_END(c_tail);
                     }
-                    fold32_f8<96>(tf, vb, mf);
-                } else {
-                    // software pipeline over the four 32-column chunks: the load of chunk c+1 is in flight while chunk c folds
-                    int va[32], vb[32];
-                    tmem_ld32(t0, va);
-                    tmem_ld_wait(va);
-                    tmem_ld32(t0 + 32, vb);
-                    fold32(tot, 0, va, mm);
-                    tmem_ld_wait(vb);
-                    tmem_ld32(t0 + 64, va);
-                    fold32(tot, 32, vb, mm);
-                    tmem_ld_wait(va);
-                    tmem_ld32(t0 + 96, vb);
-                    fold32(tot, 64, va, mm);
-                    tmem_ld_wait(vb);
-                    fold32(tot, 96, vb, mm);
-                }
-                if constexpr (!F8) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
-                        else      mbar_arrive(empty_bar0 + buf * 8u);
-                    }
                 }
                 if constexpr (F8) {
-                    if (++since == recenter_every || ag == n_ag - 1) { recenter(tf, carry); since = 0; }
+                    since += cnt;
+                    if (since >= recenter_every || ag + 4 >= n_ag) {
+                        RQ_CYC_BEGIN(c_rec);
+                        recenter(tf, carry_smem); since = 0; ++n_rec;
+                        RQ_CYC_END(c_rec);
+                    }
                 }
             }
             if (!ok) break;
@@ -482,52 +570,74 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (lane == 0 && prm.status != nullptr) atomicExch(prm.status, 2);
                 continue;
             }
+            RQ_CYC_BEGIN(c_fin);
             {
                 // Final scaling y = ((float(total) * 16) * u) * s_w and the store.  A thread owns a token's 128 outputs,
                 // but a row-per-thread store would scatter 16-byte pieces over 32 rows: the warp transposes 32 x 32
                 // pieces through shared memory (16-byte chunks XOR-swizzled by row, conflict-free both ways), after which
                 // eight lanes write 128 contiguous bytes of a row and apply s_w, which is per column.
                 const float ut = row_ok ? __ldg(prm.u + row) : 0.0f;
-                float * stg = reinterpret_cast<float *>(smem_raw + (ring - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) + e * 1024;
                 const int jj = lane & 7, rsub = lane >> 3;
+                // the row units of all four column pieces, requested before anything else: one load latency per unit
                 const bool sw_vec = (reinterpret_cast<uintptr_t>(prm.sw) & 15) == 0;
+                // weight row of this half's 32-column piece c: a pair's instruction interleaves 64-row runs of its two CTAs
+                auto piece_col = [&](int c) -> int {
+                    return n_tile * BN + (PAIR ? (c >> 1) * 128 + half * 64 + (c & 1) * 32 : half * 128 + c * 32) + jj * 4;
+                };
+                float sc[4][4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int ncol = piece_col(c);
+                    if (sw_vec && ncol + 3 < prm.N) {
+                        const float4 q = __ldg(reinterpret_cast<const float4 *>(prm.sw + ncol));
+                        sc[c][0] = q.x; sc[c][1] = q.y; sc[c][2] = q.z; sc[c][3] = q.w;
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) sc[c][k] = ncol + k < prm.N ? __ldg(prm.sw + ncol + k) : 0.0f;
+                    }
+                }
+                // the carry words come back into registers (the fold's load buffers are free now) before the tile is reused
+                uint32_t carry[F8 ? 32 : 1];
+                if constexpr (F8) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) carry[i] = carry_smem[i * 32];
+                    __syncwarp();
+                }
+                // float(total) without integer conversions (they run at a quarter of the FMA rate): the digit byte becomes
+                // the mantissa of 2^23 + digit with one byte permute, both parts are made floats by exact subtractions, and
+                // one fused multiply-add forms digit * 2^20 + low with the single round-to-nearest an int -> float
+                // conversion of the total would make.  Every re-centring left the digit at 4.
+                const float dsub = 8388608.0f + (float) (4 * n_rec);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int i = c * 32 + j * 4;
-                        int P = F8 ? carry[F8 ? i >> 2 : 0] : 0;      // four signed byte digits, units of 2^20
                         float f[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            int total;
-                            if (F8) {
-                                const int d = (int) (signed char) (P & 0xFF);
-                                total = d * (1 << 20) + (__float_as_int(tf[F8 ? i + k : 0]) - FOLD_MAGIC_BITS);
-                                P = (P - d) >> 8;
+                            float totalf;
+                            if constexpr (F8) {
+                                uint32_t w[2];
+                                unpack2(tf[F8 ? (i + k) >> 1 : 0], w[0], w[1]);
+                                const float df = __fsub_rn(__uint_as_float(prmt(carry[F8 ? i >> 2 : 0], 0x4B000000u, 0x7650u | (uint32_t) k)), dsub);
+                                const float lowf = __fsub_rn(__uint_as_float(w[k & 1]), 12582912.0f);
+                                totalf = __fmaf_rn(df, 1048576.0f, lowf);
                             } else {
-                                total = tot[F8 ? 0 : i + k];
+                                totalf = (float) tot[F8 ? 0 : i + k];
                             }
-                            f[k] = __fmul_rn(__fmul_rn((float) total, 16.0f), ut);
+                            f[k] = __fmul_rn(__fmul_rn(totalf, 16.0f), ut);
                         }
                         *reinterpret_cast<float4 *>(stg + lane * 32 + ((j ^ (lane & 7)) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
                     }
                     __syncwarp();
-                    const int ncol = n_tile * BN + half * 128 + c * 32 + jj * 4;
-                    float sc[4];
-                    if (sw_vec && ncol + 3 < prm.N) {
-                        const float4 q = __ldg(reinterpret_cast<const float4 *>(prm.sw + ncol));
-                        sc[0] = q.x; sc[1] = q.y; sc[2] = q.z; sc[3] = q.w;
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) sc[k] = ncol + k < prm.N ? __ldg(prm.sw + ncol + k) : 0.0f;
-                    }
+                    const int ncol = piece_col(c);
 #pragma unroll
                     for (int it8 = 0; it8 < 8; ++it8) {
                         const int rr = it8 * 4 + rsub;
                         const int grow = m_tile * BM + quarter * 32 + rr;
                         const float4 q = *reinterpret_cast<const float4 *>(stg + rr * 32 + ((jj ^ (rr & 7)) << 2));
-                        const float o0 = __fmul_rn(q.x, sc[0]), o1 = __fmul_rn(q.y, sc[1]), o2 = __fmul_rn(q.z, sc[2]), o3 = __fmul_rn(q.w, sc[3]);
+                        const float o0 = __fmul_rn(q.x, sc[c][0]), o1 = __fmul_rn(q.y, sc[c][1]), o2 = __fmul_rn(q.z, sc[c][2]), o3 = __fmul_rn(q.w, sc[c][3]);
                         if (grow < prm.M) {
                             // destination 0 is this GPU's buffer; N-sharded ranks get the same 128-byte row pieces straight
                             // into their copies of the output while the MMAs of the next unit run
@@ -547,9 +657,11 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     __syncwarp();
                 }
             }
+            RQ_CYC_END(c_fin);
         }
         RQ_CYC_END(c_epi);
-        if (warp == 4 && lane == 0) { RQ_CYC_REPORT(prm.status, 0x45, c_tfull); RQ_CYC_REPORT(prm.status, 0x46, c_epi); }
+        if (warp == 4 && lane == 0) { RQ_CYC_REPORT(prm.status, 0x45, c_tfull); RQ_CYC_REPORT(prm.status, 0x46, c_epi); RQ_CYC_REPORT(prm.status, 0x49, c_hold);
+                                      RQ_CYC_REPORT(prm.status, 0x4a, c_rec); RQ_CYC_REPORT(prm.status, 0x4b, c_fin); RQ_CYC_REPORT(prm.status, 0x4c, c_tail); }
     }
 
     tc_fence_before();
@@ -568,15 +680,16 @@ typedef CUresult (*encode_fn_t)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, 
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 encode_fn_t get_encode() {
-    static encode_fn_t fn = nullptr;
-    if (fn == nullptr) {
+    // resolved once; the initialisation of a function-local static is thread-safe
+    static const encode_fn_t fn = []() -> encode_fn_t {
         void * p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess) {
-            fn = reinterpret_cast<encode_fn_t>(p);
+            return reinterpret_cast<encode_fn_t>(p);
         }
-    }
+        return nullptr;
+    }();
     return fn;
 }
 
@@ -640,19 +753,26 @@ static cudaError_t launch_tc(const CUtensorMap & ta, const CUtensorMap & tb, con
 cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, int64_t K, int64_t N,
                               const int8_t * a8, const int32_t * msh, const float * u, int64_t M, int G,
                               float * y, int64_t ldy, int32_t * status, cudaStream_t stream, float * const * y_more, int n_more) {
+    // first use on a device (normally rq_w4a4_prepare's, outside stream capture); several host threads may get here at once
+    static std::mutex mu;
     static bool configured[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 64 && !configured[dev]) {
-        e = rq_configure_gemm_tc();
-        if (e != cudaSuccess) return e;
-        e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    int sms;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[dev]) {
+            e = rq_configure_gemm_tc();
+            if (e != cudaSuccess) return e;
+            e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess) return e;
+            configured[dev] = true;
+        }
+        sms = sm_count[dev] > 0 ? sm_count[dev] : 148;
     }
-    const int sms = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
     alignas(64) CUtensorMap ta, tb;
     if (rq_encode_tmap_i8(&ta, a8, K, M, BM) != 0) return cudaErrorInvalidValue;
     memcpy(&tb, tmap_w8, sizeof(tb));
@@ -660,8 +780,14 @@ cudaError_t rq_launch_gemm_tc(const void * tmap_w8, const float * sw, int fmt, i
     prm.sw = sw; prm.msh = msh; prm.u = u; prm.y = y; prm.ldy = ldy; prm.status = status;
     prm.K = (int) K; prm.N = (int) N; prm.M = (int) M; prm.G = G;
     prm.n_more = n_more;
-    for (int d = 0; d < RQ_MAX_RANKS - 1; ++d) prm.y_more[d] = d < n_more ? y_more[d] : nullptr;
-    static const int no_pair = getenv("RQ_TUNE_TC_NOPAIR") ? atoi(getenv("RQ_TUNE_TC_NOPAIR")) : 0;
+    // 16-byte stores only when every destination allows them (a peer's buffer may be aligned differently from ours)
+    bool vec = (ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+    for (int d = 0; d < RQ_MAX_RANKS - 1; ++d) {
+        prm.y_more[d] = d < n_more ? y_more[d] : nullptr;
+        if (d < n_more) vec = vec && (reinterpret_cast<uintptr_t>(y_more[d]) & 15) == 0;
+    }
+    prm.vec = vec ? 1 : 0;
+    static const int no_pair = rq_env_int("RQ_TUNE_TC_NOPAIR", 0);
     const bool pair = M > BM && !no_pair;      // a second token tile exists: let two CTAs share the weight slices
     const bool f8 = fmt == RQ_FMT_E4M3;
     if (n_more > 0) {

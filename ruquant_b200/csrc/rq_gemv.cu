@@ -17,6 +17,8 @@
 // the quantizer that precedes it.
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "rq_common.cuh"
 
 namespace {
@@ -339,36 +341,45 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
 
 template <int NT, int GS, bool HAS_K, bool ONE, bool PUSH>
 cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
+    // first use of this instantiation on a device; several host threads may get here at once
+    static std::mutex mu;
     static bool configured[64] = {};
     static int per_sm[64] = {};
     const size_t smem = (size_t) STAGES * ST_BYTES + 2 * (size_t) CONSUMERS * 32 * 4 * NT * sizeof(int);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-        if (e != cudaSuccess) return e;
-        // persistent grid: as many CTAs as are resident at once
-        int nb = 0, sms = 148;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, (CONSUMERS + 1) * 32, smem);
-        if (e != cudaSuccess) return e;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        per_sm[dev] = (nb > 0 ? nb : 1) * sms;
-        configured[dev] = true;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    int resident_slots;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[dev]) {
+            e = cudaFuncSetAttribute(rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+            if (e != cudaSuccess) return e;
+            // persistent grid: as many CTAs as are resident at once
+            int nb = 0, sms = 148;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, (CONSUMERS + 1) * 32, smem);
+            if (e != cudaSuccess) return e;
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            per_sm[dev] = (nb > 0 ? nb : 1) * sms;
+            configured[dev] = true;
+        }
+        resident_slots = per_sm[dev];
     }
     cudaLaunchConfig_t cfg = {};
     const int tiles = prm.tile_start[prm.n_jobs];
     // The quantizer ahead of this kernel (a cluster of up to 8 CTAs per token) still holds its shared memory when this
     // grid starts: CTAs beyond the free slots would start only after it, with their whole share of tiles still to do.
-    static const int reserve = getenv("RQ_TUNE_GEMV_RESERVE") ? atoi(getenv("RQ_TUNE_GEMV_RESERVE")) : 8;
-    const int resident = (dev < 64 ? per_sm[dev] : 148) - reserve;
+    static const int reserve = rq_env_int("RQ_TUNE_GEMV_RESERVE", 8);
+    const int resident = resident_slots - reserve;
     cfg.gridDim = dim3((unsigned) (tiles < resident ? tiles : resident));
     cfg.blockDim = dim3((CONSUMERS + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = getenv("RQ_NO_PDL") ? 0 : 1;
+    static const int pdl = getenv("RQ_NO_PDL") ? 0 : 1;      // read once
+    attr[0].val.programmaticStreamSerializationAllowed = pdl;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, rq_gemv_mma_kernel<NT, GS, HAS_K, ONE, PUSH>, prm);
