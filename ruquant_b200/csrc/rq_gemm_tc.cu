@@ -59,8 +59,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#ifdef RQ_TC_WAIT_HINT
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t) RQ_TC_WAIT_HINT) : "memory");
+#else
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#endif
     return ok != 0;
 }
 // bounded wait: false when the barrier did not flip within WAIT_CYCLES or another role already gave up
@@ -107,7 +112,8 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
 }
 // instruction descriptor, kind::i8: D = s32 (2 at [4,6)), A and B signed int8 (1 at [7,10) and [10,13)), both
 // K-major (0 at 15, 16), N >> 3 at [17,23), M >> 4 at [24,29)
-constexpr int BNI = BN / 2;     // weight rows per MMA instruction: a tile's 256 rows go through two instructions with accumulators of their own
+constexpr int BNI = BN;         // weight rows per MMA instruction (two instructions of 128 with accumulators of their own ran slower:
+                                // each re-reads the 128 x 32 token operand, 72 cycles per instruction against 150 for one of 256)
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
 // kind::f8f6f4: D = f32 (1 at [4,6)), A and B e4m3 (0 at [7,10) and [10,13)), K-major, same N and M fields
 constexpr uint32_t IDESC_F8 = (1u << 4) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) (BM >> 4) << 24);
@@ -115,7 +121,7 @@ constexpr uint32_t IDESC_F8 = (1u << 4) | ((uint32_t) (BNI >> 3) << 17) | ((uint
 constexpr uint32_t IDESC_PAIR = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) ((2 * BM) >> 4) << 24);
 constexpr uint32_t IDESC_F8_PAIR = (1u << 4) | ((uint32_t) (BNI >> 3) << 17) | ((uint32_t) ((2 * BM) >> 4) << 24);
 
-// One instruction of K = 32 (128 tokens x 128 weight rows, or 256 x 128 for a pair).  ACC selects between starting and
+// One instruction of K = 32 (128 tokens x 256 weight rows, or 256 x 256 for a pair).  ACC selects between starting and
 // continuing an accumulator as two separate instructions with constant predicates: the issuing thread is the
 // bottleneck of this kernel the moment it spends more than an instruction's 128 cycles between two issues, so nothing
 // is computed per instruction that a template can decide.
@@ -263,7 +269,7 @@ struct TcParams {
 
 struct __align__(8) TcShared {
     uint64_t full[MAX_STAGES], empty[MAX_STAGES];
-    uint64_t tmem_full[4], tmem_empty[4];       // [accumulator buffer 0/1][half of the tile's weight rows 0/1]
+    uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -297,8 +303,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&sh.full[s]), 1); mbar_init(smem_u32(&sh.empty[s]), 1); }
-        // half an accumulator buffer is free when its 4 epilogue warps (of BOTH CTAs of a pair, on rank 0's barrier) have arrived
-        for (int b = 0; b < 4; ++b) { mbar_init(smem_u32(&sh.tmem_full[b]), 1); mbar_init(smem_u32(&sh.tmem_empty[b]), PAIR ? 8 : 4); }
+        // a pair's accumulator buffer is free when the 8 epilogue warps of BOTH CTAs have arrived (on rank 0's barrier)
+        for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&sh.tmem_full[b]), 1); mbar_init(smem_u32(&sh.tmem_empty[b]), PAIR ? 16 : 8); }
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -398,37 +404,28 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const uint32_t buf = gcount & 1u;
-#pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            // The tile's 256 weight rows are two instructions of 128 with accumulators, barriers and epilogue
-                            // warps of their own: the first half is handed over while the second is still being multiplied.
-                            // A pair's instruction takes 64 rows from each CTA: its halves are rows {0-63, 128-191} and
-                            // {64-127, 192-255} of the tile.
-                            const uint32_t q = buf * 2u + (uint32_t) hf;
-                            const uint32_t d = tmem_base + q * BNI;
-                            const uint64_t dbh = db + (uint64_t) (hf * ((PAIR ? BH_BYTES / 2 : BH_BYTES) >> 4));
-                            if (gs == 0) {
-                                RQ_CYC_BEGIN(c_tmem);
-                                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_empty[q]), ((gcount >> 1) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
-                                RQ_CYC_END(c_tmem);
-                                tc_fence_after();
-                                RQ_CYC_BEGIN(c_issue);
-                                umma<F8, PAIR, false>(d, da + h * 4, dbh + h * 4);          // bytes >> 4 inside the swizzled row
-                            } else {
-                                RQ_CYC_BEGIN(c_issue);
-                                umma<F8, PAIR, true>(d, da + h * 4, dbh + h * 4);
-                            }
-                            umma<F8, PAIR, true>(d, da + h * 4 + 2, dbh + h * 4 + 2);
-                            RQ_CYC_END(c_issue);
-                            if (gs + 1u == gsteps_u) {
-                                RQ_CYC_BEGIN(c_commit);
-                                if (PAIR) umma_commit_pair(smem_u32(&sh.tmem_full[q]));
-                                else      umma_commit(smem_u32(&sh.tmem_full[q]));
-                                RQ_CYC_END(c_commit);
-                            }
+                        const uint32_t d = tmem_base + buf * BN;
+                        if (gs == 0) {
+                            RQ_CYC_BEGIN(c_tmem);
+                            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_empty[buf]), ((gcount >> 1) & 1u) ^ 1u, abort_flag))) { ok = false; break; }
+                            RQ_CYC_END(c_tmem);
+                            tc_fence_after();
+                            RQ_CYC_BEGIN(c_issue);
+                            umma<F8, PAIR, false>(d, da + h * 4, db + h * 4);          // bytes >> 4 inside the swizzled row
+                        } else {
+                            RQ_CYC_BEGIN(c_issue);
+                            umma<F8, PAIR, true>(d, da + h * 4, db + h * 4);
                         }
-                        if (!ok) break;
-                        if (++gs == gsteps_u) { gs = 0; ++gcount; }
+                        umma<F8, PAIR, true>(d, da + h * 4 + 2, db + h * 4 + 2);
+                        RQ_CYC_END(c_issue);
+                        if (++gs == gsteps_u) {
+                            gs = 0;
+                            RQ_CYC_BEGIN(c_commit);
+                            if (PAIR) umma_commit_pair(smem_u32(&sh.tmem_full[buf]));
+                            else      umma_commit(smem_u32(&sh.tmem_full[buf]));
+                            RQ_CYC_END(c_commit);
+                            ++gcount;
+                        }
                     }
                     if (!ok) break;
                     RQ_CYC_BEGIN(c_commit);
@@ -454,9 +451,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t lane_base = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (half * 128);
         // the quantizer records the format it wrote: refuse to multiply the wrong one
         const bool fmt_ok = prm.status == nullptr || prm.status[1] == (F8 ? RQ_FMT_E4M3 : RQ_FMT_I8);
-        // this half's barriers: index buffer * 2 + half
-        const uint32_t empty_bar0 = (PAIR ? map_to_cta(smem_u32(&sh.tmem_empty[0]), 0) : smem_u32(&sh.tmem_empty[0])) + (uint32_t) half * 8u;
-        const uint32_t full_bar0 = smem_u32(&sh.tmem_full[0]) + (uint32_t) half * 8u;
+        const uint32_t empty_bar0 = PAIR ? map_to_cta(smem_u32(&sh.tmem_empty[0]), 0) : smem_u32(&sh.tmem_empty[0]);
+        const uint32_t full_bar0 = smem_u32(&sh.tmem_full[0]);
         // groups between two re-centrings of the float totals: a multiple of four (the loop below walks four groups at a time)
         const int recenter_every = prm.G >= 256 ? 4 : RECENTER_INPUTS / prm.G;
         const bool vec = prm.vec != 0;
@@ -508,7 +504,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             // last piece of this group folds, so a warp never sits out a whole load latency.
             int va[32], vb[32];
             RQ_CYC_BEGIN(c_tfull);
-            if (!__all_sync(0xffffffffu, mbar_wait(full_bar0 + (gcount & 1u) * 16u, (gcount >> 1) & 1u, abort_flag))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(full_bar0 + (gcount & 1u) * 8u, (gcount >> 1) & 1u, abort_flag))) { ok = false; break; }
             RQ_CYC_END(c_tfull);
             tc_fence_after();
             tmem_ld32(lane_base + (gcount & 1u) * BN, va);
@@ -536,8 +532,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) {
-                            if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 16u);
-                            else      mbar_arrive(empty_bar0 + buf * 16u);
+                            if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
+                            else      mbar_arrive(empty_bar0 + buf * 8u);
                         }
                         RQ_CYC_END(c_hold);
                         RQ_CYC_BEGIN(c_tail);
@@ -545,7 +541,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         if (ag + j + 1 < n_ag) {
                             // the loads are warp-collective: leave the loop together or not at all
                             RQ_CYC_BEGIN(c_tfull);
-                            ok = __all_sync(0xffffffffu, mbar_wait(full_bar0 + (gcount & 1u) * 16u, (gcount >> 1) & 1u, abort_flag));
+                            ok = __all_sync(0xffffffffu, mbar_wait(full_bar0 + (gcount & 1u) * 8u, (gcount >> 1) & 1u, abort_flag));
                             RQ_CYC_END(c_tfull);
                             if (ok) {
                                 tc_fence_after();
@@ -578,24 +574,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // eight lanes write 128 contiguous bytes of a row and apply s_w, which is per column.
                 const float ut = row_ok ? __ldg(prm.u + row) : 0.0f;
                 const int jj = lane & 7, rsub = lane >> 3;
-                // the row units of all four column pieces, requested before anything else: one load latency per unit
                 const bool sw_vec = (reinterpret_cast<uintptr_t>(prm.sw) & 15) == 0;
-                // weight row of this half's 32-column piece c: a pair's instruction interleaves 64-row runs of its two CTAs
-                auto piece_col = [&](int c) -> int {
-                    return n_tile * BN + (PAIR ? (c >> 1) * 128 + half * 64 + (c & 1) * 32 : half * 128 + c * 32) + jj * 4;
-                };
-                float sc[4][4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int ncol = piece_col(c);
-                    if (sw_vec && ncol + 3 < prm.N) {
-                        const float4 q = __ldg(reinterpret_cast<const float4 *>(prm.sw + ncol));
-                        sc[c][0] = q.x; sc[c][1] = q.y; sc[c][2] = q.z; sc[c][3] = q.w;
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) sc[c][k] = ncol + k < prm.N ? __ldg(prm.sw + ncol + k) : 0.0f;
-                    }
-                }
+                auto piece_col = [&](int c) -> int { return n_tile * BN + half * 128 + c * 32 + jj * 4; };
                 // the carry words come back into registers (the fold's load buffers are free now) before the tile is reused
                 uint32_t carry[F8 ? 32 : 1];
                 if constexpr (F8) {
@@ -608,6 +588,20 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // one fused multiply-add forms digit * 2^20 + low with the single round-to-nearest an int -> float
                 // conversion of the total would make.  Every re-centring left the digit at 4.
                 const float dsub = 8388608.0f + (float) (4 * n_rec);
+                {
+                // the row units of all four column pieces, requested before anything else: one load latency per unit
+                float sc[4][4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int ncol = piece_col(c);
+                    if (sw_vec && ncol + 3 < prm.N) {
+                        const float4 q = __ldg(reinterpret_cast<const float4 *>(prm.sw + ncol));
+                        sc[c][0] = q.x; sc[c][1] = q.y; sc[c][2] = q.z; sc[c][3] = q.w;
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) sc[c][k] = ncol + k < prm.N ? __ldg(prm.sw + ncol + k) : 0.0f;
+                    }
+                }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
 #pragma unroll
@@ -655,6 +649,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         }
                     }
                     __syncwarp();
+                }
                 }
             }
             RQ_CYC_END(c_fin);
