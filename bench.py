@@ -229,6 +229,8 @@ def run_ours(args):
             print("pushed outputs unavailable (%s); using the NCCL all-gather" % why, file=sys.stderr)
     if push is None:
         y_arena = torch.empty((L * world * n_layer_local,), device=dev, dtype=torch.float32)
+    # the M = 4096 pass over the same stack needs the tensor-core operand of every weight as well (1 byte per weight)
+    stack_layouts = rq.PREPACK_DECODE if (args.no_prefill or args.no_prefill_stack) else rq.PREPACK_ALL
     x_off = 0
     for layer in range(L):
         # the layer's seven local outputs sit side by side, so that one all-gather assembles the layer's output
@@ -253,7 +255,7 @@ def run_ours(args):
                 ti = [n for n, _k, _n in LAYER].index(name)
                 nl = N // world
                 blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=100000 * layer + 100 * ti + rank, device=dev)
-                w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_DECODE)
+                w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=stack_layouts)
                 w.blocks = None      # the kernels read only the prepacked stream
                 del blocks
                 y_loc = y_layer_loc[col:col + nl].view(1, nl)
@@ -281,12 +283,13 @@ def run_ours(args):
         for K, x, ws, members, gather, dst in sel:
             weights = [m[2] for m in members]
             outs = [m[3] for m in members]
+            if not quantize:           # the GEMV launches alone, on this rank's shards: no exchange
+                rq.mul_mat_quantized(weights, 1, ws, out=outs, act_group=64, stream=stream)
+                continue
             if dst is not None:
                 rq.mul_mat_push(weights, x, dst, [m[1] for m in members], clip=1.0, act_group=64, workspace=ws, stream=stream)
-            elif quantize:
-                rq.mul_mat(weights, x, out=outs, clip=1.0, act_group=64, workspace=ws, stream=stream)
             else:
-                rq.mul_mat_quantized(weights, 1, ws, out=outs, act_group=64, stream=stream)
+                rq.mul_mat(weights, x, out=outs, clip=1.0, act_group=64, workspace=ws, stream=stream)
             if gather is not None:       # end of a layer: every rank gets every rank's slice of the layer's output
                 if push is not None:
                     rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
@@ -320,7 +323,7 @@ def run_ours(args):
             push["check"] = "FAILED: pushed outputs differ from the all-gathered ones (or a barrier timed out)"
             if rank == 0:
                 print(push["check"], file=sys.stderr)
-    g_gemv = capture(lambda: enqueue_pass(False)) if world == 1 else None
+    g_gemv = capture(lambda: enqueue_pass(False))
 
     def barrier():
         if world > 1:
@@ -354,20 +357,22 @@ def run_ours(args):
     roofline = None
     if g_gemv is not None:
         ms_gemv = timed(g_gemv.replay, args.steps, args.warmup)
-        achieved = total_bytes / (ms_gemv * 1e-3) / 1e9
-        # DRAM traffic per launch: the ncu capture of the K=5120 N=17408 launch (profiles/) read 44.65 MB for a
-        # 44.56 MB decode stream, i.e. the stream once; scaled to the stack's average launch by stream bytes
-        stream_bytes = sum(((N + 15) // 16) * 16 * K // 2 for (K, N) in mats)
+        achieved = total_bytes / world / (ms_gemv * 1e-3) / 1e9        # per GPU: each rank streams 1/world of the weights
+        # DRAM traffic per launch: an ncu capture of the K=5120 N=17408 launch read 44.65 MB for a 44.56 MB decode stream,
+        # i.e. the stream once; scaled to the stack's average launch by stream bytes
+        stream_bytes = sum(((N // world + 15) // 16) * 16 * K // 2 for (K, N) in mats)
         traffic = 1.002 * stream_bytes / len(groups)
         roofline = {"bound": "hbm", "kernel": "rq_gemv_mma_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                     "frac": achieved / hbm_peak, "peak_kind": "of " + peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                     "avg_launch_us": ms_gemv * 1e3 / len(groups), "launches_per_step": len(groups),
-                    "algorithmic_bytes_per_launch": total_bytes / len(groups), "traffic": traffic,
+                    "algorithmic_bytes_per_launch": total_bytes / world / len(groups), "traffic": traffic, "per_gpu": True,
                     "traffic_note": "dram read+write bytes per launch, ncu capture of one shape scaled by stream bytes"}
 
     # ---- end to end through the C ABI with host buffers
     x_host = torch.randn((L * k_layer,), dtype=torch.float32).pin_memory()
-    y_host = torch.empty((L * world * n_layer_local,), dtype=torch.float32).pin_memory()
+    # every rank needs all the activations; of the outputs each rank takes only its own rows' share to the host (the
+    # gathered copy on the device is what the next node would read)
+    y_host = torch.empty((L, n_layer_local) if world > 1 else (L * n_layer_local,), dtype=torch.float32).pin_memory()
     h2d = x_host.numel() * 4
     d2h = y_host.numel() * 4
 
@@ -395,21 +400,24 @@ def run_ours(args):
             ev_done[i].record(stream)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_done[i])
-                y_host[a * y_layer:b * y_layer].copy_(y_arena[a * y_layer:b * y_layer], non_blocking=True)
+                if world > 1:
+                    y_host[a:b].copy_(y_arena.view(L, world, n_layer_local)[a:b, rank], non_blocking=True)
+                else:
+                    y_host[a * y_layer:b * y_layer].copy_(y_arena[a * y_layer:b * y_layer], non_blocking=True)
         stream.wait_stream(s_out)
 
     ms_e2e = timed(e2e_step, args.steps, args.warmup)
     e2e = {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "ms_per_step": ms_e2e, "copy_overlap": "%d layer chunks, copies on two streams beside the compute" % n_chunks}
+           "ms_per_step": ms_e2e, "copy_overlap": "%d layer chunks, copies on two streams beside the compute" % n_chunks,
+           "per_rank": "every rank copies all activations in and its own share of the outputs out" if world > 1 else None}
 
     # ---- prefill: the M = 4096 gate/up-shaped and down-shaped GEMMs, whole node and GEMM kernel alone
     prefill = None
     if not args.no_prefill:
-        def prefill_leg(K, N, M, seed):
+        def prefill_leg(K, N, M, seed, with_cpu):
             nl = N // world
             blocks = synth.random_weights(nl, K, rq.TYPE_W4A4H, seed=seed + rank, device=dev)
             w = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, K, N=nl, layouts=rq.PREPACK_PREFILL)
-            del blocks
             g = torch.Generator(device=dev)
             g.manual_seed(99)
             x = torch.randn((M, K), generator=g, device=dev, dtype=torch.float32)
@@ -434,10 +442,17 @@ def run_ours(args):
                 if world > 1:
                     dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
 
+            def local_node():        # this rank's share without the exchange: the compute-only curve
+                rq.mul_mat(w, x, out=y, clip=1.0, act_group=64, workspace=ws, stream=stream)
+
             def gemm_only():
                 rq.mul_mat_quantized(w, M, ws, out=y, act_group=64, stream=stream)
 
-            ms_node = timed(node, max(3, args.steps), 3)
+            def nofold():
+                rq.tc_nofold_probe(w, M, ws, y, stream=stream)
+
+            reps = max(3, args.steps)
+            ms_node = timed(node, reps, 3)
             if dst is not None:
                 # the pushed [M][N] must hold, in this rank's columns, what the plain node computes, on every rank
                 torch.cuda.synchronize()
@@ -455,17 +470,120 @@ def run_ours(args):
                     push["check"] = "FAILED: prefill pushed output differs from the all-gathered one"
                     if rank == 0:
                         print(push["check"], file=sys.stderr)
-            ms_gemm = timed(gemm_only, max(3, args.steps), 3)
+            ms_local = timed(local_node, reps, 3) if world > 1 else ms_node
+            ms_gemm = timed(gemm_only, reps, 3)
+            ms_probe = timed(nofold, reps, 3)
+            with torch.cuda.stream(stream):
+                local_node()             # leave a real result in y for the checks below
+            stream.synchronize()
             rq.device_status(ws, K, M)
             ops = 2.0 * M * N * K
-            return {"workload": "W4A4H K=%d N=%d M=%d" % (K, N, M), "tops_node": ops / (ms_node * 1e-3) / 1e12, "ms_node": ms_node,
-                    "tops_gemm_kernel": 2.0 * M * nl * K / (ms_gemm * 1e-3) / 1e12 * world, "ms_gemm_kernel": ms_gemm,
-                    "int8_dense_peak_nominal_tops": 4500.0 * world,
-                    "frac_of_nominal_int8_peak": ops / (ms_node * 1e-3) / 1e12 / (4500.0 * world)}
+            tops_gemm = 2.0 * M * nl * K / (ms_gemm * 1e-3) / 1e12 * world
+            tops_probe = 2.0 * M * nl * K / (ms_probe * 1e-3) / 1e12 * world
+            out = {"workload": "W4A4H K=%d N=%d M=%d" % (K, N, M), "tops_node": ops / (ms_node * 1e-3) / 1e12, "ms_node": ms_node,
+                   "ms_node_compute_only": ms_local, "tops_node_compute_only": ops / (ms_local * 1e-3) / 1e12,
+                   "nvlink_bytes_out_per_rank": (world - 1) * M * nl * 4,
+                   "tops_gemm_kernel": tops_gemm, "ms_gemm_kernel": ms_gemm,
+                   "int8_dense_peak_nominal_tops": 4500.0 * world,
+                   "frac_of_nominal_int8_peak": ops / (ms_node * 1e-3) / 1e12 / (4500.0 * world),
+                   # the dominant kernel against the tensor-core bound: nominal dense 8-bit peak, and what this kernel's own
+                   # TMA / tcgen05 / TMEM pipeline reaches in the same run with the per-group fold left out (one
+                   # accumulator over all of K: rq_w4a4_tc_nofold_probe)
+                   "roofline": {"bound": "tensor", "kernel": "rq_gemm_tc_kernel", "achieved": tops_gemm, "peak": 4500.0 * world,
+                                "unit": "TOP/s", "frac": tops_gemm / (4500.0 * world), "peak_kind": "nominal dense int8/fp8 (no measured 8-bit peak in MEASURED_PEAKS.json)",
+                                "peak_measured_nofold": tops_probe, "frac_of_measured_nofold": tops_gemm / tops_probe,
+                                "algorithmic_ops_per_launch": 2.0 * M * nl * K, "fold_fmas_per_launch": M * nl * K / 64.0,
+                                "avg_launch_us": ms_gemm * 1e3, "traffic": None}}
+            if with_cpu and world == 1:
+                # end to end through the C ABI with host buffers: x from pinned host memory, y back to it, every step
+                xh = x.cpu().pin_memory()
+                yh = torch.empty((M, nl), dtype=torch.float32).pin_memory()
+
+                def e2e_node():
+                    x.copy_(xh, non_blocking=True)
+                    rq.mul_mat(w, x, out=y, clip=1.0, act_group=64, workspace=ws, stream=stream)
+                    yh.copy_(y, non_blocking=True)
+
+                ms_e2e_p = timed(e2e_node, reps, 3)
+                out["e2e"] = {"value": ops / (ms_e2e_p * 1e-3) / 1e12, "unit": "TOP/s", "ms_per_step": ms_e2e_p,
+                              "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * nl * 4}
+                if not args.no_cpu:
+                    # the reference's CPU node on the first 64 tokens (its scalar dot product makes 4096 tokens a matter of
+                    # minutes); every output of those tokens is also compared with what the GPU left in y
+                    import oracle
+                    tok = 64
+                    wb_host = blocks.cpu().numpy()
+                    x_host = xh[:tok].numpy()
+                    impl, kind = (oracle.Ref(), "reference") if oracle.have_ref() else (oracle.Port(), "port")
+                    threads = os.cpu_count() or 1
+                    best, y_cpu = float("inf"), None
+                    for _ in range(2):
+                        t0 = time.perf_counter()
+                        y_cpu = impl.mul_mat(wb_host, 45, K, x_host, threads=threads)
+                        best = min(best, time.perf_counter() - t0)
+                    same = bool((y_cpu.view("uint32") == yh[:tok].numpy().view("uint32")).all())
+                    out["cpu_baseline"] = {"value": 2.0 * tok * N * K / best / 1e12, "unit": "TOP/s", "cores": threads, "kind": kind,
+                                           "sample": "first %d of %d tokens, best of 2; %.3f s measured, %.1f s for all tokens by linear "
+                                                     "extrapolation" % (tok, M, best, best * M / tok),
+                                           "bit_identical_to_gpu_on_sample": same}
+            del blocks
+            return out
 
         _, K, N, M = PREFILL
-        prefill = prefill_leg(K, N, M, 424242)
-        prefill["down_shaped"] = prefill_leg(N, K, M, 434343)      # K = 17408 (68 x 256 rotation), N = 5120
+        prefill = prefill_leg(K, N, M, 424242, True)
+        prefill["down_shaped"] = prefill_leg(N, K, M, 434343, False)      # K = 17408 (68 x 256 rotation), N = 5120
+
+    # ---- configuration 5 at M = 4096: one pass over the whole stack (1.787e14 operations at 64 layers).  The linears are
+    # not chained: every activation width has one seeded N(0,1) input, every output width one buffer.  N-sharded ranks
+    # assemble each matmul's output with an NCCL all-gather (the exchange BASELINE.json's configuration names).
+    prefill_stack = None
+    if not args.no_prefill and not args.no_prefill_stack:
+        Mp = PREFILL[3]
+        xs, wss, ys, yg = {}, {}, {}, {}
+        for names in GROUPS:
+            K = LAYER_DIMS[names[0]][0]
+            if K not in xs:
+                g = torch.Generator(device=dev)
+                g.manual_seed(4096 + K)
+                xs[K] = torch.randn((Mp, K), generator=g, device=dev, dtype=torch.float32)
+                wss[K] = rq.new_workspace(K, Mp, dev)
+            for name in names:
+                N = LAYER_DIMS[name][1]
+                if N not in ys:
+                    ys[N] = torch.empty((Mp, N // world), device=dev, dtype=torch.float32)
+                    if world > 1:
+                        yg[N] = torch.empty((world, Mp, N // world), device=dev, dtype=torch.float32)
+
+        def stack_pass(gather):
+            for K, _x, _ws, members, _g, _dst in groups:
+                weights = [m[2] for m in members]
+                outs = [ys[m[0]] for m in members]
+                rq.mul_mat(weights, xs[K], out=outs, clip=1.0, act_group=64, path=rq.PATH_TC, workspace=wss[K], stream=stream)
+                if gather and world > 1:
+                    for m in members:
+                        dist.all_gather_into_tensor(yg[m[0]].view(-1), ys[m[0]].view(-1))
+
+        ops_stack = sum(2.0 * Mp * N * K for (K, N) in mats)
+        ms_stack = timed(lambda: stack_pass(True), 2, 1)
+        ms_stack_local = timed(lambda: stack_pass(False), 2, 1) if world > 1 else ms_stack
+        for K in wss:
+            rq.device_status(wss[K], K, Mp)
+        prefill_stack = {"workload": "%d-layer stack, M=%d prefill, 7 matmuls per layer (%.4g operations per pass)" % (L, Mp, ops_stack),
+                         "ms_per_pass": ms_stack, "tops": ops_stack / (ms_stack * 1e-3) / 1e12,
+                         "ms_per_pass_compute_only": ms_stack_local, "tops_compute_only": ops_stack / (ms_stack_local * 1e-3) / 1e12,
+                         "frac_of_nominal_int8_peak": ops_stack / (ms_stack * 1e-3) / 1e12 / (4500.0 * world),
+                         "nvlink_bytes_in_per_rank_per_pass": (world - 1) * sum(Mp * (N // world) * 4 for (_k, N) in mats),
+                         "exchange": "none" if world == 1 else "ncclAllGather per matmul output"}
+        del xs, wss, ys, yg
+
+    # ---- the reference's own performance shapes (one GPU): decode widths in GB/s, 512 tokens in TOPS
+    perf_shapes = None
+    if rank == 0 and world == 1 and not args.no_perf_shapes:
+        perf_shapes = []
+        for rows, tokens, K in REF_PERF_SHAPES:
+            r = time_shape(K, rows, tokens, rq.TYPE_W4A4H, 0, 64, 5, 2, probe=False)
+            perf_shapes.append({"rows": rows, "tokens": tokens, "K": K, "us_node": r["us_node"], "us_contraction": r["us_contraction"],
+                                "GBps_node": r["GBps_node"], "frac_hbm_node": r["frac_hbm_node"], "TOPS_node": r["TOPS_node"]})
 
     # ---- CPU baseline beside it (rank 0, one GPU): one layer on the host cores
     cpu = None
@@ -489,10 +607,15 @@ def run_ours(args):
                                            "N-sharded x%d, GEMV epilogues store into every rank's output over NVLink, one barrier kernel "
                                            "per layer (check against an NCCL all-gather: %s)" % (world, push.get("check", "equal")) if push is not None else
                                            "N-sharded x%d, one NCCL all-gather per layer output" % world),
-                           "cuda_graph": True},
+                           "cuda_graph": True,
+                           "reference_arm": "bench.py --impl reference times 1 of the 64 layers per step on the host cores (GB/s is "
+                                            "per-layer bytes / per-layer time, so the two arms' values compare; their ms_per_step do not)"},
                 "frac_of_hbm_peak": value / (hbm_peak * world), "peak_kind": "of " + peak_kind,
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "prefill": prefill, "clocks": clocks,
-                "gpu_launches": 2 * len(groups) * args.steps}
+                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "prefill": prefill, "prefill_stack": prefill_stack,
+                "reference_perf_shapes": perf_shapes, "clocks": clocks,
+                # kernels of this library launched inside the timed decode region: a rotate+quantize and a GEMV per
+                # activation group, and one barrier kernel per layer when the ranks push their outputs
+                "gpu_launches": (2 * len(groups) + (L if push is not None else 0)) * args.steps}
         print(json.dumps(line))
     if world > 1:
         # every rank is past its last collective: leave without tearing NCCL down under the captured graphs
@@ -551,22 +674,20 @@ def run_wquant(args):
                       "bit_identical_on_sample": same}))
 
 
-def run_single(args):
-    """One shape, K,N,M[,type]: a CUDA graph of back-to-back matmuls over enough distinct weight copies to overflow
-    L2 (the method of the reference's own bench, rig/ggml_bench.cpp), whole node and contraction kernel alone."""
+def time_shape(K, N, M, type_, path, G, steps, warmup, copies=0, probe=True):
+    """One shape: a CUDA graph of back-to-back matmuls over enough distinct weight copies to overflow L2 (the method of
+    the reference's own bench, rig/ggml_bench.cpp), whole node, contraction kernel alone, rotate+quantize alone."""
     import torch
 
     import ruquant_b200 as rq
     from ruquant_b200 import synth
 
-    parts = [int(v) for v in args.single.split(",")]
-    K, N, M = parts[:3]
-    type_ = parts[3] if len(parts) > 3 else rq.TYPE_W4A4H
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", torch.cuda.current_device())
     wbytes = N * (K // 256) * 144
-    copies = args.copies if args.copies > 0 else max(1, -(-(384 << 20) // wbytes)) if M <= 64 else 1
-    layouts = rq.PREPACK_ALL if args.path == 0 else (rq.PREPACK_DECODE if args.path == 1 else rq.PREPACK_PREFILL)
+    copies = copies if copies > 0 else max(1, -(-(384 << 20) // wbytes)) if M <= 64 else 1
+    layouts = rq.PREPACK_ALL if path == 0 else (rq.PREPACK_DECODE if path == 1 else rq.PREPACK_PREFILL)
+    if path == 0:
+        layouts = rq.PREPACK_DECODE if M <= 64 else rq.PREPACK_PREFILL
     base = synth.random_weights(N, K, type_, seed=1, device=dev)
     weights = []
     for c in range(copies):
@@ -579,19 +700,22 @@ def run_single(args):
     y = torch.empty((M, N), device=dev, dtype=torch.float32)
     ws = rq.new_workspace(K, M, dev)
     stream = torch.cuda.Stream(device=dev)
-    G = args.group
 
     def node():
         for w in weights:
-            rq.mul_mat(w, x, out=y, clip=1.0, act_group=G, path=args.path, workspace=ws, stream=stream)
+            rq.mul_mat(w, x, out=y, clip=1.0, act_group=G, path=path, workspace=ws, stream=stream)
 
     def contraction():
         for w in weights:
-            rq.mul_mat_quantized(w, M, ws, out=y, act_group=G, path=args.path, stream=stream)
+            rq.mul_mat_quantized(w, M, ws, out=y, act_group=G, path=path, stream=stream)
 
     def quant_only():
         for w in weights:
-            rq.quantize(x, w.n_rot, 1.0, G, workspace=ws, stream=stream, fmt=rq.act_format(w, M, args.path))
+            rq.quantize(x, w.n_rot, 1.0, G, workspace=ws, stream=stream, fmt=rq.act_format(w, M, path))
+
+    def nofold():
+        for w in weights:
+            rq.tc_nofold_probe(w, M, ws, y, stream=stream)
 
     def timed(fn):
         g = torch.cuda.CUDAGraph()
@@ -600,36 +724,49 @@ def run_single(args):
             stream.synchronize()
             with torch.cuda.graph(g, stream=stream):
                 fn()
-            for _ in range(args.warmup):
+            for _ in range(warmup):
                 g.replay()
             stream.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
-            for _ in range(args.steps):
+            for _ in range(steps):
                 g.replay()
             e1.record(stream)
             stream.synchronize()
-        return e0.elapsed_time(e1) * 1e3 / args.steps / copies      # us per matmul
-
-    def nofold():
-        for w in weights:
-            rq.tc_nofold_probe(w, M, ws, y, stream=stream)
+        return e0.elapsed_time(e1) * 1e3 / steps / copies      # us per matmul
 
     us_node, us_con, us_q = timed(node), timed(contraction), timed(quant_only)
     us_probe = None
-    if layouts & rq.PREPACK_PREFILL and (args.path == 2 or M > 64):
-        quant_only()                  # leave an activation of the right format in the workspace
+    if probe and layouts & rq.PREPACK_PREFILL and (path == 2 or M > 64):
+        with torch.cuda.stream(stream):
+            quant_only()              # leave an activation of the right format in the workspace
         us_probe = timed(nofold)
     rq.device_status(ws, K, M)
     hbm_peak, _, kind = measured_peaks()
     ab, ops = algorithmic_bytes(K, N, M), 2.0 * M * N * K
-    print(json.dumps({"single": {"K": K, "N": N, "M": M, "type": type_, "group": G, "path": args.path, "copies": copies},
-                      "us_node": us_node, "us_contraction": us_con, "us_rotate_quantize": us_q,
-                      "GBps_node": ab / us_node / 1e3, "GBps_contraction": ab / us_con / 1e3,
-                      "frac_hbm_node": ab / us_node / 1e3 / hbm_peak, "frac_hbm_contraction": ab / us_con / 1e3 / hbm_peak,
-                      "TOPS_node": ops / us_node / 1e6, "TOPS_contraction": ops / us_con / 1e6,
-                      "us_nofold_probe": us_probe, "TOPS_nofold_probe": (ops / us_probe / 1e6) if us_probe else None,
-                      "peak_kind": "of " + kind}))
+    return {"single": {"K": K, "N": N, "M": M, "type": type_, "group": G, "path": path, "copies": copies},
+            "us_node": us_node, "us_contraction": us_con, "us_rotate_quantize": us_q,
+            "GBps_node": ab / us_node / 1e3, "GBps_contraction": ab / us_con / 1e3,
+            "frac_hbm_node": ab / us_node / 1e3 / hbm_peak, "frac_hbm_contraction": ab / us_con / 1e3 / hbm_peak,
+            "TOPS_node": ops / us_node / 1e6, "TOPS_contraction": ops / us_con / 1e6,
+            "us_nofold_probe": us_probe, "TOPS_nofold_probe": (ops / us_probe / 1e6) if us_probe else None,
+            "peak_kind": "of " + kind}
+
+
+def run_single(args):
+    """K,N,M[,type]: time one shape instead of the stack."""
+    import torch
+    parts = [int(v) for v in args.single.split(",")]
+    K, N, M = parts[:3]
+    type_ = parts[3] if len(parts) > 3 else 45
+    torch.cuda.set_device(0)
+    print(json.dumps(time_shape(K, N, M, type_, args.path, args.group, args.steps, args.warmup, args.copies)))
+
+
+# the reference's own performance cases for these types (tests/test-backend-ops.cpp hunk in
+# patches/llama.cpp-ruquant.patch:3067-3074): (rows, tokens, K)
+REF_PERF_SHAPES = [(17408, n, 5120) for n in (1, 8, 16, 512)] + [(5120, n, 17408) for n in (1, 8, 16, 512)] + \
+                  [(6144, n, 5120) for n in (1, 8, 16, 512)]
 
 
 def main():
@@ -641,6 +778,8 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-prefill-stack", action="store_true", help="skip the M = 4096 pass over the whole stack")
+    ap.add_argument("--no-perf-shapes", action="store_true", help="skip the reference's own performance shapes")
     ap.add_argument("--single", default="", help="K,N,M[,type]: time one shape instead of the stack")
     ap.add_argument("--wquant", default="", help="K,N[,type[,wgroup]]: time the GPU weight quantizer beside the reference's CPU code")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"], help="N > 1: how a layer's output is assembled")

@@ -153,11 +153,13 @@ def workspace_bytes(K, M):
 
 
 def new_workspace(K, M, device="cuda"):
-    """A workspace for M tokens of width K with its status block zeroed (the error word in it is sticky)."""
+    """A workspace for M tokens of width K with its status block zeroed (the error word in it is sticky).  Waits for
+    the zeroing to finish, so that the workspace may be used on any stream afterwards."""
     import torch
     ws = torch.empty(workspace_bytes(K, M), dtype=torch.uint8, device=device)
     with torch.cuda.device(ws.device):
         _check(lib().rq_w4a4_workspace_init(ws.data_ptr(), K, M, _stream_ptr()), "rq_w4a4_workspace_init")
+        torch.cuda.current_stream().synchronize()
     return ws
 
 

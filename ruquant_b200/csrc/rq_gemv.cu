@@ -372,6 +372,7 @@ cudaError_t launch_one(const GemvParams & prm, cudaStream_t stream) {
     // grid starts: CTAs beyond the free slots would start only after it, with their whole share of tiles still to do.
     static const int reserve = rq_env_int("RQ_TUNE_GEMV_RESERVE", 8);
     const int resident = resident_slots - reserve;
+    // (an evenly divided grid -- every CTA the same number of tiles -- measured slower: 3.79 against 3.68 ms per pass)
     cfg.gridDim = dim3((unsigned) (tiles < resident ? tiles : resident));
     cfg.blockDim = dim3((CONSUMERS + 1) * 32);
     cfg.dynamicSmemBytes = smem;
