@@ -433,7 +433,25 @@ def run_ours(args):
             elif world > 1:
                 y_all = torch.empty((world, M, nl), device=dev, dtype=torch.float32)
 
+            # N > 1: the ranks share the rotate+quantize work too -- rank r does tokens [r*M/g, (r+1)*M/g), the ranks exchange
+            # the one-byte codes, group multipliers and token units (M*K bytes and a little, a quarter of what x itself
+            # would take; identical bits by construction), then every rank multiplies all tokens by its own rows
+            share = world > 1 and dst is not None and M % world == 0 and not args.replicated_quantizer
+            if share:
+                a8v, mshv, uv = rq.workspace_views(ws, K, M, 64)
+                t0, t1 = rank * (M // world), (rank + 1) * (M // world)
+                slabs = [(a8v, torch.empty_like(a8v[t0:t1])), (mshv, torch.empty_like(mshv[t0:t1])), (uv, torch.empty_like(uv[t0:t1]))]
+                fmt = rq.act_format(w, M)
+
             def node():
+                if share:
+                    rq.quantize_rows(x[t0:t1], M, t0, w.n_rot, 1.0, 64, fmt, ws, stream=stream)
+                    for region, tmp in slabs:
+                        tmp.copy_(region[t0:t1])
+                        dist.all_gather_into_tensor(region.view(-1), tmp.view(-1))
+                    rq.mul_mat_push([w], None, dst, [N], act_group=64, workspace=ws, stream=stream, M=M)
+                    rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
+                    return
                 if dst is not None:
                     rq.mul_mat_push([w], x, dst, [N], clip=1.0, act_group=64, workspace=ws, stream=stream)
                     rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
@@ -483,6 +501,9 @@ def run_ours(args):
             out = {"workload": "W4A4H K=%d N=%d M=%d" % (K, N, M), "tops_node": ops / (ms_node * 1e-3) / 1e12, "ms_node": ms_node,
                    "ms_node_compute_only": ms_local, "tops_node_compute_only": ops / (ms_local * 1e-3) / 1e12,
                    "nvlink_bytes_out_per_rank": (world - 1) * M * nl * 4,
+                   "quantizer": "shared: each rank quantizes M/%d tokens, codes exchanged (%d bytes in per rank)" % (
+                       world, (world - 1) * (M // world) * (K + 4 * (K // 64) + 4)) if (world > 1 and dst is not None and M % world == 0 and
+                                                                                      not args.replicated_quantizer) else "replicated on every rank",
                    "tops_gemm_kernel": tops_gemm, "ms_gemm_kernel": ms_gemm,
                    "int8_dense_peak_nominal_tops": 4500.0 * world,
                    "frac_of_nominal_int8_peak": ops / (ms_node * 1e-3) / 1e12 / (4500.0 * world),
@@ -576,6 +597,53 @@ def run_ours(args):
                          "exchange": "none" if world == 1 else "ncclAllGather per matmul output"}
         del xs, wss, ys, yg
 
+    # ---- the reference's own tensor-parallel mode for attn_output / ffn_down: weights split along K (block-diagonal
+    # rotation, `--rot-blocks`), every rank multiplies its slice of x by its block columns, the partial outputs are added in
+    # rank order over peer-mapped buffers (rq_w4a4_sum_partials) -- beside the N-split of the same shapes above
+    k_split = None
+    if world > 1 and push is not None and not args.no_prefill:
+        k_split = []
+        symm = push["symm"]
+        for name in ("o", "down"):
+            K, N = LAYER_DIMS[name]
+            ks = K // world
+            if ks % 256 or rq.hadamard_factor(ks) is None:
+                continue
+            blocks = synth.random_weights(N, ks, rq.TYPE_W4A4H, seed=515151 + rank, device=dev)     # a slice is a W4A4H tensor of its own
+            wk_ = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, ks, N=N, layouts=rq.PREPACK_ALL)
+            del blocks
+            for Mk in (1, PREFILL[3]):
+                g = torch.Generator(device=dev)
+                g.manual_seed(777 + rank)
+                xk = torch.randn((Mk, ks), generator=g, device=dev, dtype=torch.float32)
+                part = symm.empty(Mk * N, dtype=torch.float32, device=dev)
+                ph = symm.rendezvous(part, dist.group.WORLD)
+                yk = torch.empty((Mk, N), device=dev, dtype=torch.float32)
+                wsk = rq.new_workspace(ks, Mk, dev)
+                pptrs = [int(p) for p in ph.buffer_ptrs]
+                yptrs = [yk.data_ptr() if r == rank else 0 for r in range(world)]
+
+                def knode():
+                    rq.mul_mat(wk_, xk, out=part.view(Mk, N), clip=1.0, act_group=64, workspace=wsk, stream=stream)
+                    rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
+                    rq.sum_partials(pptrs, rank, Mk * N, yptrs, stream=stream)
+                    rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)    # partials free again
+
+                def klocal():
+                    rq.mul_mat(wk_, xk, out=part.view(Mk, N), clip=1.0, act_group=64, workspace=wsk, stream=stream)
+
+                reps = max(3, args.steps)
+                ms_k = timed(knode, reps, 3)
+                ms_kl = timed(klocal, reps, 3)
+                # all ranks must hold the same bits
+                chk = [torch.empty_like(yk) for _ in range(world)]
+                dist.all_gather(chk, yk)
+                same = all(bool((c.view(torch.int32) == yk.view(torch.int32)).all().item()) for c in chk) and int(push["status"].item()) == 0
+                k_split.append({"tensor": name, "K": K, "N": N, "M": Mk, "ms_node": ms_k, "ms_node_compute_only": ms_kl,
+                                "nvlink_bytes_in_per_rank": (world - 1) * Mk * N * 4, "all_ranks_bit_identical": same,
+                                "n_split_nvlink_bytes_out_per_rank": (world - 1) * Mk * (N // world) * 4})
+            del wk_
+
     # ---- the reference's own performance shapes (one GPU): decode widths in GB/s, 512 tokens in TOPS
     perf_shapes = None
     if rank == 0 and world == 1 and not args.no_perf_shapes:
@@ -612,7 +680,7 @@ def run_ours(args):
                                             "per-layer bytes / per-layer time, so the two arms' values compare; their ms_per_step do not)"},
                 "frac_of_hbm_peak": value / (hbm_peak * world), "peak_kind": "of " + peak_kind,
                 "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "prefill": prefill, "prefill_stack": prefill_stack,
-                "reference_perf_shapes": perf_shapes, "clocks": clocks,
+                "reference_perf_shapes": perf_shapes, "k_split": k_split, "clocks": clocks,
                 # kernels of this library launched inside the timed decode region: a rotate+quantize and a GEMV per
                 # activation group, and one barrier kernel per layer when the ranks push their outputs
                 "gpu_launches": (2 * len(groups) + (L if push is not None else 0)) * args.steps}
@@ -779,6 +847,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-prefill-stack", action="store_true", help="skip the M = 4096 pass over the whole stack")
+    ap.add_argument("--replicated-quantizer", action="store_true", help="N > 1 prefill: every rank quantizes all tokens (no exchange of codes)")
     ap.add_argument("--no-perf-shapes", action="store_true", help="skip the reference's own performance shapes")
     ap.add_argument("--single", default="", help="K,N,M[,type]: time one shape instead of the stack")
     ap.add_argument("--wquant", default="", help="K,N[,type[,wgroup]]: time the GPU weight quantizer beside the reference's CPU code")

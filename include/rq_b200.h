@@ -151,6 +151,15 @@ int rq_w4a4_rotate(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64
 int rq_w4a4_quantize(const float * x_dev, int64_t ldx, int64_t M, int64_t K, int64_t n_rot, float clip, int act_group,
                      int act_format, void * workspace_dev, size_t workspace_bytes, void * stream);
 
+/* The same for `count` tokens starting at token `first` of a workspace laid out for M_total tokens (x_rows_dev points at
+ * the first of those rows).  Ranks that share the quantizer's work each do a range of tokens this way and exchange the
+ * results -- the three regions of rq_w4a4_workspace_layout are contiguous per token range: count * K bytes of codes,
+ * count * (K / act_group) multipliers, count units -- before every rank multiplies by its own rows
+ * (rq_w4a4_mul_mat_quantized, or rq_w4a4_mul_mat_push with x_dev = NULL). */
+int rq_w4a4_quantize_rows(const float * x_rows_dev, int64_t ldx, int64_t M_total, int64_t first, int64_t count, int64_t K,
+                          int64_t n_rot, float clip, int act_group, int act_format, void * workspace_dev,
+                          size_t workspace_bytes, void * stream);
+
 /* The activation format (RQ_FMT_*) the contraction of these weights at M tokens wants -- what rq_w4a4_mul_mat passes
  * to the quantizer itself; for callers that run rq_w4a4_quantize and rq_w4a4_mul_mat_quantized separately.
  * Negative rq_status on a request that cannot be served (missing layout, weights that need different formats). */
@@ -171,7 +180,8 @@ int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * str
  * writes them itself).  rq_w4a4_mul_mat_push is rq_w4a4_mul_mat (GEMV up to 64 tokens: needs the decode layout; tcgen05
  * kernel above: needs the prefill layout) whose epilogue stores every output value into n_dst buffers instead of one: y_dst[d * n_w + i] is weight i's output in destination d
  * -- this rank's own buffer and the peer-mapped buffers of the other ranks (cudaIpc / symmetric memory), all with the
- * same row stride ldy[i].  No collective kernel follows.  rq_rank_barrier then makes the pushed data of all ranks
+ * same row stride ldy[i].  x_dev may be NULL: the workspace then already holds the quantized activation of all M tokens
+ * (rq_w4a4_quantize / rq_w4a4_quantize_rows in the format rq_w4a4_act_format names).  No collective kernel follows.  rq_rank_barrier then makes the pushed data of all ranks
  * visible: rank r stores a fresh epoch into word r of every rank's flag array (flags_of_rank[p] = rank p's array of
  * n_ranks words, peer-mapped, zero-initialised) and waits, bounded, until its own array shows that epoch from every
  * rank; the epoch counts up in *epoch_dev (local device memory, zero-initialised), so a captured graph replays
@@ -192,6 +202,19 @@ int rq_w4a4_mul_mat_push(const rq_weight_desc * const * w, int n_w, const float 
                          void * workspace_dev, size_t workspace_bytes, void * stream);
 int rq_rank_barrier(uint32_t * const * flags_of_rank, int rank, int n_ranks, uint32_t * epoch_dev, int32_t * status_dev,
                     void * stream);
+
+/* K-split ranks of one node (the reference's tensor-parallel mode for attn_output / ffn_down: `ruquant convert
+ * --rot-blocks`, src/convert.rs:120-128; every rank multiplies its block columns by its slice of x and the partial
+ * outputs are added by a peer-write all-reduce, patches/mx-llama.cpp-ruquant.patch:5293-5374).  Each rank's partial
+ * [count] f32 lies in a buffer every rank has mapped: partials_of_rank[r] is rank r's as mapped here, 16-byte aligned.
+ * The sum is taken in rank order, ((p0 + p1) + p2) + ..., so every rank gets the same bits.  two_shot = 0: this rank adds
+ * all `count` elements into y_of_rank[rank] (its own, local) -- one kernel, nothing after it.  two_shot = 1: this rank
+ * adds its 1/n_ranks piece and stores it into every y_of_rank[d] (peer-mapped outputs); an rq_rank_barrier after it makes
+ * all pieces visible on all ranks.  Either way an rq_rank_barrier must stand between the MUL_MATs that wrote the
+ * partials and this call, and the partials must not be overwritten before every rank's sum has run (a second barrier,
+ * or two sets of buffers).  Capture-safe. */
+int rq_w4a4_sum_partials(const float * const * partials_of_rank, int rank, int n_ranks, int64_t count,
+                         float * const * y_of_rank, int two_shot, void * stream);
 
 /* The reference's weight quantizer on the GPU: N rows of K fp32 (rows ldw floats apart) -> N rows of K/256 blocks,
  * byte for byte what quantize_w4a4 / quantize_w4a4h write (patch:2775-2789; per row quantize_row_w4a4_ref /

@@ -10,7 +10,7 @@ the command line), writes them verbatim, between a small prelude and a threaded 
 `oracle/_ref/ruquant_ref.c` (git-ignored), and compiles that one file with gcc the way ggml-base is compiled
 (-O3 -std=gnu11, no -march, so no FMA contraction).  No reference line is stored in this repository.
 
-Usage: python oracle/build_ref.py [/path/to/reference]   (default: $RQ_REFERENCE_DIR, else REFERENCE_DIR below)
+Usage: python oracle/build_ref.py [/path/to/reference]   (default: $RQ_REFERENCE_DIR, else a `reference` directory beside this repository)
 """
 import os
 import subprocess
@@ -111,7 +111,7 @@ def _balanced(lines):
     return text.count("{") == text.count("}")
 
 
-REFERENCE_DIR = "/root/reference"
+REFERENCE_DIR = os.path.normpath(os.path.join(HERE, "..", "..", "reference"))      # the reference tree checked out beside this repository
 
 
 def main():

@@ -23,7 +23,7 @@ EXPORTS = [
     "rq_w4a4_quantize", "rq_w4a4_workspace_layout", "rq_w4a4_device_status", "rq_status_string", "rq_last_cuda_error",
     "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n", "rq_w4a4_act_format",
     "rq_w4a4_quantize_weights", "rq_w4a4_quantize_weights_scratch_bytes", "rq_w4a4_mul_mat_push", "rq_rank_barrier",
-    "rq_w4a4_workspace_init", "rq_w4a4_tc_nofold_probe",
+    "rq_w4a4_workspace_init", "rq_w4a4_tc_nofold_probe", "rq_w4a4_sum_partials", "rq_w4a4_quantize_rows",
 ]
 
 
@@ -76,6 +76,7 @@ def lib():
         L.rq_w4a4_rotate.argtypes = [vp, i64, i64, i64, i64, vp, i64, vp]
         L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, i32, vp, sz, vp]
         L.rq_w4a4_act_format.argtypes = [ctypes.POINTER(pd), i32, i64, i32]
+        L.rq_w4a4_quantize_rows.argtypes = [vp, i64, i64, i64, i64, i64, i64, f32, i32, i32, vp, sz, vp]
         L.rq_w4a4_mul_mat_push.argtypes = [ctypes.POINTER(pd), i32, vp, i64, i64, ctypes.POINTER(vp), i32, ctypes.POINTER(i64), f32,
                                            i32, vp, sz, vp]
         L.rq_rank_barrier.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vp, vp]
@@ -86,6 +87,7 @@ def lib():
         L.rq_w4a4_workspace_layout.argtypes = [i64, i64, i32, u64p, u64p, u64p, u64p]
         L.rq_w4a4_device_status.argtypes = [vp, i64, i64, vp]
         L.rq_w4a4_workspace_init.argtypes = [vp, i64, i64, vp]
+        L.rq_w4a4_sum_partials.argtypes = [ctypes.POINTER(vp), i32, i32, i64, ctypes.POINTER(vp), i32, vp]
         L.rq_w4a4_tc_nofold_probe.argtypes = [pd, i64, vp, i64, vp, sz, vp]
         L.rq_status_string.argtypes = [i32]
         L.rq_status_string.restype = ctypes.c_char_p
@@ -205,12 +207,38 @@ def mul_mat(weights, x, out=None, clip=None, act_group=None, path=PATH_AUTO, wor
     return outs[0] if single else outs
 
 
-def mul_mat_push(weights, x, dst_ptrs, ldy, clip=None, act_group=None, workspace=None, stream=None):
+def _mul_mat_push_quantized(ws_list, M, dst_ptrs, ldy, act_group, workspace, stream):
+    import torch
+    n_w, n_dst = len(ws_list), len(dst_ptrs)
+    if act_group is None:
+        act_group = lib().rq_w4a4_act_group()
+    with torch.cuda.device(workspace.device):
+        pd = ctypes.POINTER(WeightDesc)
+        descs = (pd * n_w)(*[ctypes.pointer(w.desc) for w in ws_list])
+        ys = (ctypes.c_void_p * (n_w * n_dst))(*[dst_ptrs[d][i] for d in range(n_dst) for i in range(n_w)])
+        lds = (ctypes.c_int64 * n_w)(*ldy)
+        _check(lib().rq_w4a4_mul_mat_push(descs, n_w, None, 0, M, ys, n_dst, lds, 1.0, act_group, workspace.data_ptr(),
+                                          workspace.numel(), _stream_ptr(stream)), "rq_w4a4_mul_mat_push")
+    return workspace
+
+
+def quantize_rows(x_rows, M_total, first, n_rot, clip, group, fmt, workspace, stream=None):
+    """Rotate and quantize the tokens x_rows [count, K] into rows first .. first+count of a workspace laid out for M_total."""
+    import torch
+    count, K = x_rows.shape
+    with torch.cuda.device(x_rows.device):
+        _check(lib().rq_w4a4_quantize_rows(x_rows.data_ptr(), x_rows.stride(0), M_total, first, count, K, n_rot, clip, group, fmt,
+                                           workspace.data_ptr(), workspace.numel(), _stream_ptr(stream)), "rq_w4a4_quantize_rows")
+
+
+def mul_mat_push(weights, x, dst_ptrs, ldy, clip=None, act_group=None, workspace=None, stream=None, M=None):
     """The decode-path node writing every output into several buffers: dst_ptrs[d][i] is the device address of weight
     i's output in destination d (this rank's own buffer first, then the peer-mapped buffers of the other ranks)."""
     import torch
     ws_list = [weights] if isinstance(weights, Weight) else list(weights)
     n_w, n_dst = len(ws_list), len(dst_ptrs)
+    if x is None:        # the workspace already holds the quantized activation of M tokens
+        return _mul_mat_push_quantized(ws_list, M, dst_ptrs, ldy, act_group, workspace, stream)
     K, M = ws_list[0].K, x.shape[0]
     if clip is None:
         clip = ws_list[0].clip()
@@ -235,6 +263,15 @@ def rank_barrier(flag_ptrs, rank, epoch, status=None, stream=None):
     arr = (ctypes.c_void_p * n)(*flag_ptrs)
     _check(lib().rq_rank_barrier(arr, rank, n, epoch.data_ptr(), status.data_ptr() if status is not None else None,
                                  _stream_ptr(stream)), "rq_rank_barrier")
+
+
+def sum_partials(partial_ptrs, rank, count, y_ptrs, two_shot=False, stream=None):
+    """K-split ranks: the rank-ordered sum of the ranks' partial outputs.  partial_ptrs[r] / y_ptrs[r]: device addresses,
+    as mapped on this rank, of rank r's partial and output (one shot needs only y_ptrs[rank])."""
+    n = len(partial_ptrs)
+    parts = (ctypes.c_void_p * n)(*partial_ptrs)
+    ys = (ctypes.c_void_p * n)(*[p if p else None for p in y_ptrs])
+    _check(lib().rq_w4a4_sum_partials(parts, rank, n, count, ys, 1 if two_shot else 0, _stream_ptr(stream)), "rq_w4a4_sum_partials")
 
 
 def mul_mat_static(weight, x, out=None, clip=None, act_group=None, path=PATH_AUTO, stream=None):

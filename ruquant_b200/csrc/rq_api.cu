@@ -283,6 +283,35 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize(const flo
     return RQ_OK;
 }
 
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_quantize_rows(const float * x_rows_dev, int64_t ldx, int64_t M_total, int64_t first, int64_t count,
+                                     int64_t K, int64_t n_rot, float clip, int act_group, int act_format, void * workspace_dev,
+                                     size_t workspace_bytes, void * stream) {
+    if (act_format != RQ_FMT_I8 && act_format != RQ_FMT_E4M3) return RQ_ERR_ARG;
+    if (first < 0 || count < 1 || first + count > M_total) return RQ_ERR_SHAPE;
+    int rc = rq_check_x(x_rows_dev, ldx, count, K);
+    if (rc != RQ_OK) return rc;
+    if (act_group != 64 && act_group != 128 && act_group != 256) return RQ_ERR_GROUP;
+    if (!(clip > 0.0f) || isinf(clip)) return RQ_ERR_CLIP;
+    const rq_ws_layout l = rq_ws(K, M_total);
+    if (workspace_dev == nullptr || workspace_bytes < l.bytes || (reinterpret_cast<uintptr_t>(workspace_dev) & 255) != 0)
+        return RQ_ERR_WORKSPACE;
+    int p = 1, m = 0;
+    float scale = 1.0f;
+    if (n_rot > 0) {
+        if (K % n_rot != 0 || !rq_hadamard_factor(n_rot, &p, &m)) return RQ_ERR_ROTATION;
+        scale = 1.0f / sqrtf((float) n_rot);
+    } else if (n_rot < 0) {
+        return RQ_ERR_ROTATION;
+    }
+    uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
+    RQ_CUDA(rq_launch_act(x_rows_dev, ldx, count, K, (int) n_rot, p, m, scale, clip, act_group, act_format,
+                          reinterpret_cast<int8_t *>(ws + l.off_a8) + first * K,
+                          reinterpret_cast<int32_t *>(ws + l.off_msh) + first * (K / act_group),
+                          reinterpret_cast<float *>(ws + l.off_u) + first, nullptr, 0,
+                          reinterpret_cast<int32_t *>(ws + l.off_status), (cudaStream_t) stream));
+    return RQ_OK;
+}
+
 // which kernel a weight takes at M tokens: true = tcgen05 GEMM, false = GEMV passes; -1 on a bad request
 static int rq_use_tc(const rq_weight_desc * w, int64_t M, int path) {
     const bool has_dec = (w->layouts & RQ_PREPACK_DECODE) != 0, has_pre = (w->layouts & RQ_PREPACK_PREFILL) != 0;
@@ -432,10 +461,14 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_mul_mat_push(const
         for (int d = 0; d < n_dst; ++d) if (y_dst[d * n_w + i] == nullptr) return RQ_ERR_ARG;
     }
     const int fmt = tc && !w[0]->wk_mode ? RQ_FMT_E4M3 : RQ_FMT_I8;
-    int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group, fmt,
-                              workspace_dev, workspace_bytes, stream);
-    if (rc != RQ_OK) return rc;
     const rq_ws_layout l = rq_ws(w[0]->K, M);
+    if (x_dev != nullptr) {
+        int rc = rq_w4a4_quantize(x_dev, ldx, M, w[0]->K, w[0]->type == RQ_TYPE_W4A4H ? w[0]->n_rot : 0, clip, act_group, fmt,
+                                  workspace_dev, workspace_bytes, stream);
+        if (rc != RQ_OK) return rc;
+    } else if (workspace_dev == nullptr || workspace_bytes < l.bytes) {     // the activation is already in the workspace
+        return RQ_ERR_WORKSPACE;
+    }
     uint8_t * ws = static_cast<uint8_t *>(workspace_dev);
     if (tc) {
         for (int i = 0; i < n_w; ++i) {
@@ -471,6 +504,30 @@ extern "C" __attribute__((visibility("default"))) int rq_rank_barrier(uint32_t *
         return RQ_ERR_ARG;
     for (int p = 0; p < n_ranks; ++p) if (flags_of_rank[p] == nullptr) return RQ_ERR_ARG;
     RQ_CUDA(rq_launch_rank_barrier(flags_of_rank, rank, n_ranks, epoch_dev, status_dev, (cudaStream_t) stream));
+    return RQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_sum_partials(const float * const * partials_of_rank, int rank, int n_ranks, int64_t count,
+                                                                         float * const * y_of_rank, int two_shot, void * stream) {
+    if (partials_of_rank == nullptr || y_of_rank == nullptr || n_ranks < 1 || n_ranks > RQ_MAX_RANKS || rank < 0 || rank >= n_ranks)
+        return RQ_ERR_ARG;
+    if (count < 1) return RQ_ERR_SHAPE;
+    for (int r = 0; r < n_ranks; ++r) {
+        if (partials_of_rank[r] == nullptr || (reinterpret_cast<uintptr_t>(partials_of_rank[r]) & 15) != 0) return RQ_ERR_ARG;
+    }
+    if (!two_shot) {
+        if (y_of_rank[rank] == nullptr || (reinterpret_cast<uintptr_t>(y_of_rank[rank]) & 15) != 0) return RQ_ERR_ARG;
+        float * out[1] = { y_of_rank[rank] };
+        RQ_CUDA(rq_launch_partial_sum(partials_of_rank, n_ranks, 0, count, out, 1, (cudaStream_t) stream));
+        return RQ_OK;
+    }
+    for (int r = 0; r < n_ranks; ++r) {
+        if (y_of_rank[r] == nullptr || (reinterpret_cast<uintptr_t>(y_of_rank[r]) & 15) != 0) return RQ_ERR_ARG;
+    }
+    // pieces of whole 4-element vectors; the last rank takes the remainder
+    const int64_t per = ((count / n_ranks) / 4) * 4;
+    const int64_t lo = per * rank, hi = rank == n_ranks - 1 ? count : per * (rank + 1);
+    RQ_CUDA(rq_launch_partial_sum(partials_of_rank, n_ranks, lo, hi, y_of_rank, n_ranks, (cudaStream_t) stream));
     return RQ_OK;
 }
 

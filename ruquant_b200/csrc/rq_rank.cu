@@ -40,7 +40,58 @@ __global__ void __launch_bounds__(32) rq_rank_barrier_kernel(const RankBarrierPa
     if (p == 0) *prm.epoch = epoch;
 }
 
+// Sum of the ranks' partial outputs for K-split weights (the reference's tensor-parallel mode for attn_output / ffn_down:
+// every rank multiplies its block columns by its slice of x, the partial Y are added; its own all-reduce writes packed
+// partials into peer staging slots and adds them behind flag barriers, k_broadcast_reduce_16 / k_twoshot_16 in
+// patches/mx-llama.cpp-ruquant.patch:5293-5374).  Here every rank's partial sits in a buffer all ranks have mapped; after
+// a rank barrier a rank reads the partials with plain peer loads and adds them IN RANK ORDER, ((p0 + p1) + p2) + ..., so
+// every rank holds the same bits and a CPU restatement can reproduce them.  Two forms:
+//   one shot   every rank adds all `count` elements itself: (g-1) * count * 4 bytes in per rank, one kernel, nothing after it;
+//   two shot   rank r adds elements [lo, hi) only and stores the sums into every rank's output (peer stores): 2 * (g-1)/g *
+//              count * 4 bytes per rank; a second rank barrier then makes all pieces visible everywhere.
+struct PartialSumParams {
+    const float * part[RQ_MAX_RANKS];   // part[r]: rank r's partial as mapped on this rank
+    float * out[RQ_MAX_RANKS];          // destinations of the sums (one shot: out[0] only)
+    int64_t lo, hi;                     // elements this rank adds
+    int n_ranks, n_out;
+};
+
+__global__ void __launch_bounds__(256) rq_partial_sum_kernel(const PartialSumParams prm) {
+    const int64_t n4 = (prm.hi - prm.lo) >> 2;          // lo and hi are multiples of 4 except for the tail of the last piece
+    const int64_t stride = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const int64_t e = prm.lo + 4 * i;
+        float4 acc = *reinterpret_cast<const float4 *>(prm.part[0] + e);
+        for (int r = 1; r < prm.n_ranks; ++r) {
+            const float4 v = *reinterpret_cast<const float4 *>(prm.part[r] + e);
+            acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+        }
+        for (int d = 0; d < prm.n_out; ++d) *reinterpret_cast<float4 *>(prm.out[d] + e) = acc;
+    }
+    // the last piece's tail
+    const int64_t t0 = prm.lo + 4 * n4;
+    for (int64_t e = t0 + (int64_t) blockIdx.x * blockDim.x + threadIdx.x; e < prm.hi; e += stride) {
+        float acc = prm.part[0][e];
+        for (int r = 1; r < prm.n_ranks; ++r) acc = __fadd_rn(acc, prm.part[r][e]);
+        for (int d = 0; d < prm.n_out; ++d) prm.out[d][e] = acc;
+    }
+}
+
 }  // namespace
+
+cudaError_t rq_launch_partial_sum(const float * const * partials, int n_ranks, int64_t lo, int64_t hi, float * const * outs, int n_out,
+                                  cudaStream_t stream) {
+    PartialSumParams prm = {};
+    for (int r = 0; r < n_ranks; ++r) prm.part[r] = partials[r];
+    for (int d = 0; d < n_out; ++d) prm.out[d] = outs[d];
+    prm.lo = lo; prm.hi = hi; prm.n_ranks = n_ranks; prm.n_out = n_out;
+    if (hi <= lo) return cudaSuccess;
+    const int64_t n4 = (hi - lo + 3) / 4;
+    int64_t blocks = (n4 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    rq_partial_sum_kernel<<<(unsigned) blocks, 256, 0, stream>>>(prm);
+    return cudaGetLastError();
+}
 
 cudaError_t rq_launch_rank_barrier(uint32_t * const * flags_of_rank, int rank, int n_ranks, uint32_t * epoch, int32_t * status,
                                    cudaStream_t stream) {

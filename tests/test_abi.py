@@ -100,3 +100,17 @@ def test_environment_switches_resolve_as_in_the_reference(env, want):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     got = subprocess.run([sys.executable, "-c", ENV_PROBE], env=e, cwd=root, capture_output=True, text=True, check=True).stdout.strip()
     assert got == want
+
+
+def test_adapter_exports_the_reference_entry_points():
+    """adapter/rq-w4a4.cu compiled against the reference's ggml headers: the six functions ggml-cuda's dispatcher calls
+    (patches/llama.cpp-ruquant.patch:2389-2401) and the custom1 launcher are defined in the object."""
+    import os
+    import subprocess
+    obj = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "adapter", "_build", "rq-w4a4.o")
+    if not os.path.exists(obj):
+        pytest.skip("adapter/_build is not built (needs the reference's ggml headers)")
+    syms = subprocess.check_output(["nm", "-C", "--defined-only", obj], text=True)
+    for name in ("ggml_cuda_rq_w4a4_supported(", "ggml_cuda_rq_w4a4_ready(", "ggml_cuda_mul_mat_rq_w4a4(", "ggml_cuda_rq_w4a4_can_fuse(",
+                 "ggml_cuda_mul_mat_rq_w4a4_fused(", "ggml_cuda_rq_graph_begin(", "rq_b200_custom1_mul_mat"):
+        assert name in syms, name

@@ -123,3 +123,30 @@ def test_push_from_every_tensor_core_variant(rq, port, wgroup, M):
         assert_bits(np.ascontiguousarray(got[:, :N]), want, "push wgroup=%d M=%d" % (wgroup, M))
         assert (got[:, N:] == -1.0).all()
     assert float(b[0].item()) == -1.0
+
+
+@pytest.mark.parametrize("M", [12, 200])
+def test_token_ranges_quantized_apart_multiply_like_the_whole(rq, port, M):
+    """Ranks that share the quantizer's work: token ranges rotated and quantized by separate rq_w4a4_quantize_rows calls
+    into one workspace (here one GPU makes both calls), then the contraction on the whole -- through
+    rq_w4a4_mul_mat_quantized and through the pushing node with no x."""
+    K, N = 5120, 320
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9850), 45)
+    w = rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    x = inputs.outlier_activations(M, K, 9851 + M)
+    xd = dev(x)
+    cut = M // 3
+    ws = rq.new_workspace(K, M)
+    fmt = rq.act_format(w, M)
+    rq.quantize_rows(xd[cut:], M, cut, w.n_rot, 1.0, 64, fmt, ws)          # the ranges in any order
+    rq.quantize_rows(xd[:cut], M, 0, w.n_rot, 1.0, 64, fmt, ws)
+    want = port.mul_mat(wb, 45, K, x)
+    y = rq.mul_mat_quantized(w, M, ws, act_group=64)
+    torch.cuda.synchronize()
+    assert_bits(y.cpu().numpy(), want, "ranges, M=%d" % M)
+    bufs = [torch.full((M, N), -1.0, dtype=torch.float32, device="cuda") for _ in range(2)]
+    rq.mul_mat_push([w], None, [[b.data_ptr()] for b in bufs], [N], act_group=64, workspace=ws, M=M)
+    torch.cuda.synchronize()
+    rq.device_status(ws, K, M)
+    for b in bufs:
+        assert_bits(b.cpu().numpy(), want, "ranges pushed, M=%d" % M)

@@ -338,21 +338,33 @@ def test_status_codes(rq, port):
 @pytest.mark.parametrize("world", [2, 4])
 def test_column_split_partials_sum_in_rank_order(rq, port, world):
     """The reference's tensor-parallel mode for attn_output / ffn_down: every rank multiplies its block columns by its
-    slice of x (quantized on its own) and the partials are summed in rank order.  One GPU plays all ranks in turn."""
+    slice of x (quantized on its own) and the partials are added in rank order by rq_w4a4_sum_partials, in one shot (every
+    rank adds everything) and in two (a rank adds its piece and stores it into every rank's output).  One GPU plays all
+    ranks in turn; 5 x 97 outputs do not divide into whole vectors per rank, so the last piece's tail is covered."""
     from ruquant_b200 import shard
-    K, N, M = 5120 * 2, 96, 5
+    K, N, M = 5120 * 2, 97, 5
     wb = port.quantize_weights(inputs.normal_weights(N, K, 9300), 45, rot_blocks=world)    # rotation length K / world
     x = inputs.outlier_activations(M, K, 9301)
     ks = K // world
-    got, want = None, None
+    parts, want = [], None
     for r in range(world):
         cols = np.ascontiguousarray(shard.col_shard(wb, N, K, r, world))
         xs = np.ascontiguousarray(x[:, r * ks:(r + 1) * ks])
-        p_gpu = torch.from_numpy(gpu_mul_mat(rq, cols, 45, ks, xs))
+        parts.append(dev(gpu_mul_mat(rq, cols, 45, ks, xs)))            # rank r's partial, "mapped" on every rank
         p_cpu = port.mul_mat(cols, 45, ks, xs)
-        got = p_gpu if got is None else got + p_gpu
         want = p_cpu if want is None else want + p_cpu
-    assert_bits(got.numpy(), want, "column split over %d" % world)
+    ptrs = [p.data_ptr() for p in parts]
+    for rank in range(world):                                            # one shot: every rank by itself
+        y = torch.full((M, N), -1.0, dtype=torch.float32, device="cuda")
+        rq.sum_partials(ptrs, rank, M * N, [y.data_ptr() if r == rank else 0 for r in range(world)])
+        torch.cuda.synchronize()
+        assert_bits(y.cpu().numpy(), want, "column split over %d, one shot, rank %d" % (world, rank))
+    ys = [torch.full((M, N), -1.0, dtype=torch.float32, device="cuda") for _ in range(world)]
+    for rank in range(world):                                            # two shots: each rank its piece into every output
+        rq.sum_partials(ptrs, rank, M * N, [t.data_ptr() for t in ys], two_shot=True)
+    torch.cuda.synchronize()
+    for rank in range(world):
+        assert_bits(ys[rank].cpu().numpy(), want, "column split over %d, two shots, rank %d" % (world, rank))
 
 
 def test_column_split_needs_rotation_blocks(rq, port):
