@@ -56,33 +56,44 @@ struct ActParams {
 // =====================================================================================  one CTA per token
 // P > 1: Paley order (compile time); P == 1: no Paley stage (plain W4A4, or a power-of-two rotation).
 // shared memory: [K floats row][P*P floats sign table]
+// three CTAs (tokens) per SM where the row fits three times in shared memory: caps the 256-thread form at 85 registers
+#ifndef RQ_ACT_MIN_CTAS
+#define RQ_ACT_MIN_CTAS 3
+#endif
 template <int P, int THREADS>
-__global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
+__global__ void __launch_bounds__(THREADS, THREADS <= 256 ? RQ_ACT_MIN_CTAS : 1) rq_act_kernel(const ActParams prm) {
     extern __shared__ __align__(16) float buf[];
     __shared__ float g_lo[512], g_hi[512];
     __shared__ float red[THREADS / 32];
     __shared__ signed char chi[128];
+    __shared__ uint64_t row_bar;
     const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const int K = prm.K;
     float * table = buf + K;
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"((uint32_t) __cvta_generic_to_shared(&row_bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    constexpr bool NEED_TABLE = P > 1 && THREADS > 256;       // the 256-thread form takes every sign from code or constant memory
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     RQ_STAMP_DECL;
     RQ_STAMP(tid == 0);                                     // 0: start
-    // pull the row towards L2 while the kernel ahead may still be running (a hint: no value is read before the wait)
-    for (int i = tid; i < K / 32; i += nt) asm volatile("prefetch.global.L2 [%0];" :: "l"(prm.x + (int64_t) t * prm.ldx + i * 32));
-    if constexpr (P > 1) build_sign_table(table, chi, P, tid, nt);
+    if constexpr (NEED_TABLE) build_sign_table(table, chi, P, tid, nt);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (t == 0 && tid == 0 && prm.status != nullptr) prm.status[1] = prm.fmt;     // word 0 (errors) is sticky: only the host clears it
     RQ_STAMP(tid == 0);                                     // 1: after the wait
 
+    // the row arrives in one bulk copy (thousands of tokens: what counts is trips to memory per token, and this is one)
     const float * xrow = prm.x + (int64_t) t * prm.ldx;
+    if (!bulk_load_row(buf, xrow, (uint32_t) K * 4u, &row_bar, tid)) {
+        if (tid == 0 && prm.status != nullptr) atomicExch(prm.status, 1);
+        return;
+    }
     if (prm.n_rot > 0) {
-        load_fwht(xrow, buf, K, prm.m, tid, nt);
+        fwht_resident(buf, K, prm.m, tid, nt);
         RQ_STAMP(tid == 0);                                 // 2: chunks transformed
-    } else {
-        for (int i = tid; i < K / 4; i += nt) reinterpret_cast<float4 *>(buf)[i] = __ldg(reinterpret_cast<const float4 *>(xrow) + i);
-        __syncthreads();
     }
 
     if (prm.n_rot > 0) {
@@ -110,8 +121,12 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
                 for (int i = 0; i < P; ++i) col[i] = b[i * m];
                 for (int a0 = 0; a0 < P; a0 += 4) {
                     float out[4];
-                    if (THREADS <= 256 && a0 > 0) paley_block4_const<P>(col, a0, prm.rot_scale, out);   // block 0 holds the irregular output 0
-                    else paley_block4<P>(col, table, a0, prm.rot_scale, out);
+                    if constexpr (THREADS <= 256) {
+                        if (a0 > 0) paley_block4_const<P>(col, a0, prm.rot_scale, out);
+                        else paley_block4_first<P>(col, prm.rot_scale, out, std::make_index_sequence<P>{});      // holds the irregular output 0
+                    } else {
+                        paley_block4<P>(col, table, a0, prm.rot_scale, out);
+                    }
 #pragma unroll
                     for (int k = 0; k < 4; ++k) b[(a0 + k) * m] = out[k];
                 }
@@ -155,7 +170,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_kernel(const ActParams prm) {
         constexpr bool F8 = decltype(f8)::value;
         for (int w = tid; w < nwords; w += nt) {
             const int g = w / lpg;
-            int mi;
+            float mi;
             const uint2 pk = encode_word<F8>(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1],
                                              g_lo[g], g_hi[g], R, unit, mi);
             const int kw = w * 8, run = kw & ~63, off = kw & 63;   // two 4-input pieces, permuted inside their run of 64
@@ -259,7 +274,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_cluster_kernel(const ActParams
             const float4 a = reinterpret_cast<float4 *>(outs)[2 * w], b = reinterpret_cast<float4 *>(outs)[2 * w + 1];
             float lo, hi;
             group_range(a, b, 8, prm.clip, lo, hi);
-            int mi;
+            float mi;
             const uint2 pk = encode_word<F8>(a, b, lo, hi, R, unit, mi);
             const int off = (w & 7) * 8;
             *reinterpret_cast<uint32_t *>(arow + kbase + rq_perm64(off)) = pk.x;
@@ -349,12 +364,13 @@ cudaError_t launch(const ActParams & prm, int64_t M, cudaStream_t stream) {
             return launch_ex(rq_act_cluster_kernel<CP, CT>, dim3((unsigned) C, (unsigned) M), dim3(CT), smem, C, stream, prm, units_max);
         }
     }
-    const size_t smem = ((size_t) K + (P > 1 ? (size_t) P * P : 0)) * sizeof(float);
+    const size_t smem_row = (size_t) K * sizeof(float);
+    const size_t smem = smem_row + (P > 1 ? (size_t) P * P : 0) * sizeof(float);       // the wide CTA keeps a sign table
     if (smem > SMEM_LIMIT) return cudaErrorInvalidValue;
     // few tokens and a cheap Paley stage: one big CTA per token keeps every phase short
     static const int wide = rq_env_int("RQ_TUNE_ACT_WIDE", 1);
     if (P <= 20 && M <= 64 && wide) return launch_ex(rq_act_kernel<(P <= 20 ? P : 1), 1024>, dim3((unsigned) M), dim3(1024), smem, 1, stream, prm);
-    return launch_ex(rq_act_kernel<P, ACT_THREADS>, dim3((unsigned) M), dim3(ACT_THREADS), smem, 1, stream, prm);
+    return launch_ex(rq_act_kernel<P, ACT_THREADS>, dim3((unsigned) M), dim3(ACT_THREADS), smem_row, 1, stream, prm);
 }
 
 }  // namespace

@@ -92,6 +92,21 @@ __device__ __forceinline__ void paley_block4_const(const float (&col)[P], int a0
     out[3] = __fmul_rn(acc3, scale);
 }
 
+// outputs 0 .. 3 of one column held in registers (the block with the matrix's irregular first row and column): the signs
+// are compile-time, so a term is one add or subtract and no table is needed
+template <int P, size_t... I>
+__device__ __forceinline__ void paley_block4_first(const float (&col)[P], float scale, float (&out)[4], std::index_sequence<I...>) {
+    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+    ((acc0 = paley_plus<P>((int) I, 0) ? __fadd_rn(acc0, col[I]) : __fsub_rn(acc0, col[I]),
+      acc1 = paley_plus<P>((int) I, 1) ? __fadd_rn(acc1, col[I]) : __fsub_rn(acc1, col[I]),
+      acc2 = paley_plus<P>((int) I, 2) ? __fadd_rn(acc2, col[I]) : __fsub_rn(acc2, col[I]),
+      acc3 = paley_plus<P>((int) I, 3) ? __fadd_rn(acc3, col[I]) : __fsub_rn(acc3, col[I])), ...);
+    out[0] = __fmul_rn(acc0, scale);
+    out[1] = __fmul_rn(acc1, scale);
+    out[2] = __fmul_rn(acc2, scale);
+    out[3] = __fmul_rn(acc3, scale);
+}
+
 // outputs a0 .. a0+3 of one column held in registers: four independent chains, terms in ascending i
 template <int P>
 __device__ __forceinline__ void paley_block4(const float (&col)[P], const float * __restrict__ table, int a0, float scale,
@@ -206,6 +221,76 @@ __device__ __forceinline__ void load_transform_runs(const float * __restrict__ s
     }
 }
 
+// the same for runs that already lie in shared memory (a bulk copy brought the row): transformed in place
+template <int EPT>
+__device__ __forceinline__ void transform_runs_inplace(float * buf, int count, int warp, int nwarps, int lane) {
+    for (int r = warp; r < count; r += nwarps) {
+        float * d = buf + (size_t) r * 32 * EPT + lane * EPT;
+        float v[EPT];
+        if constexpr (EPT >= 4) {
+#pragma unroll
+            for (int j = 0; j < EPT; j += 4) {
+                const float4 q = *reinterpret_cast<const float4 *>(d + j);
+                v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) v[j] = d[j];
+        }
+        fwht_warp<EPT>(v, lane);
+        if constexpr (EPT >= 4) {
+#pragma unroll
+            for (int j = 0; j < EPT; j += 4) *reinterpret_cast<float4 *>(d + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) d[j] = v[j];
+        }
+    }
+}
+
+// Sylvester transform, chunk by chunk, of a row that is already in shared memory.  Ends with a CTA barrier.
+__device__ __forceinline__ void fwht_resident(float * buf, int len, int m, int tid, int nt, int bar = 0) {
+    const int warp = tid >> 5, nwarps = nt >> 5, lane = tid & 31;
+    const int run = m < 1024 ? m : 1024;
+    switch (run) {
+        case 32:   if (m > 1) transform_runs_inplace<1>(buf, len / 32, warp, nwarps, lane); break;
+        case 64:   transform_runs_inplace<2>(buf, len / 64, warp, nwarps, lane); break;
+        case 128:  transform_runs_inplace<4>(buf, len / 128, warp, nwarps, lane); break;
+        case 256:  transform_runs_inplace<8>(buf, len / 256, warp, nwarps, lane); break;
+        case 512:  transform_runs_inplace<16>(buf, len / 512, warp, nwarps, lane); break;
+        case 1024: transform_runs_inplace<32>(buf, len / 1024, warp, nwarps, lane); break;
+        default:   fwht_chunks(buf, len, m, tid, nt, bar); return;      // m < 32: the generic passes
+    }
+    rq_cta_sync(bar, nt);
+    for (int ls = 10; (1 << ls) < m; ls += 3) {
+        const int rem = m >> ls;
+        if (rem >= 8) fwht_pass<8>(buf, len, ls, tid, nt);
+        else if (rem == 4) fwht_pass<4>(buf, len, ls, tid, nt);
+        else fwht_pass<2>(buf, len, ls, tid, nt);
+        rq_cta_sync(bar, nt);
+    }
+}
+
+// One bulk asynchronous copy of a row (bytes a multiple of 16, both ends 16-byte aligned) into shared memory, issued by
+// one thread, awaited by all: a single trip to memory for the whole row, where per-run loads expose one trip per round of
+// runs a warp takes.  The wait is bounded (about a second); false when it ran out.
+__device__ __forceinline__ bool bulk_load_row(float * dst, const float * src, uint32_t bytes, uint64_t * bar, int tid) {
+    const uint32_t b = (uint32_t) __cvta_generic_to_shared(bar);
+    if (tid == 0) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(b), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"((uint32_t) __cvta_generic_to_shared(dst)), "l"(src), "r"(bytes), "r"(b) : "memory");
+    }
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b) : "memory");
+        if (ok) return true;
+        if ((i & 63u) == 63u && clock64() - t0 > 2000000000ll) return false;
+    }
+}
+
 // A buffer of `len` floats made of whole chunks of m: loaded from global memory and Sylvester-transformed chunk by
 // chunk.  Chunks up to 1024 wide are done entirely in registers and shuffles; wider chunks finish their upper
 // strides (1024 and above, conflict-free) in shared memory.  Ends with a CTA barrier.
@@ -253,28 +338,55 @@ __device__ __forceinline__ void group_range(const float4 a, const float4 b, int 
 }
 
 // the 8 codes of a word and the group's multiplier.  F8 false: int8 8*(q - z) (RQ_FMT_I8); true: the e4m3 byte of
-// (q - z), exact (RQ_FMT_E4M3, the fp8 tensor-core path)
+// (q - z), exact (RQ_FMT_E4M3, the fp8 tensor-core path).  Everything stays in float registers: conversions between
+// float and int run at a quarter of the FMA rate on this part and integer logic at half of it, and this loop runs once
+// per input value.
+//   rint(t)        (t + 1.5*2^23) - 1.5*2^23: round-to-nearest-even of the add, exact for |t| < 2^22; beyond that the
+//                  result may be off by one, at magnitudes the clamp to [0, 15] that follows maps to the same end
+//   byte, int8     the low mantissa byte of 8*(q - z) + 1.5*2^23 is the value's two's-complement byte
+//   byte, e4m3     cvt.rn.satfinite.e4m3x2.f32 on two values at once (|q - z| <= 15 has four significant bits: exact)
 template <bool F8>
-__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, int & mi) {
+__device__ __forceinline__ uint2 encode_word(const float4 a, const float4 b, float lo, float hi, float R, float unit, float & mf_out) {
     const float mf = fminf(fmaxf(ceilf(__fdiv_rn(__fmul_rn(__fsub_rn(hi, lo), 255.0f), R)), 1.0f), 255.0f);
-    mi = (int) mf;
-    const float inv = __fdiv_rn(1.0f, __fmul_rn((float) mi, unit));
-    const float zf = fminf(fmaxf(rintf(__fmul_rn(-lo, inv)), 0.0f), 15.0f);
+    mf_out = mf;
+    const float inv = __fdiv_rn(1.0f, __fmul_rn(mf, unit));
+    constexpr float MAGIC = 12582912.0f;
+    const float zf = fminf(fmaxf(__fsub_rn(__fadd_rn(__fmul_rn(-lo, inv), MAGIC), MAGIC), 0.0f), 15.0f);
     const float v[8] = { a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w };
-    uint32_t pk[2] = { 0u, 0u };
+    float dz[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        const float qf = fminf(fmaxf(__fadd_rn(rintf(__fmul_rn(v[j], inv)), zf), 0.0f), 15.0f);
-        const int dz = (int) qf - (int) zf;                                  // q - z in [-15, 15]
-        const uint32_t byte = F8 ? rq_e4m3_of_int(dz) : (uint32_t) ((RQ_ACT_SCALE * dz) & 0xFF);
-        pk[j >> 2] |= byte << (8 * (j & 3));
+        const float r = __fsub_rn(__fadd_rn(__fmul_rn(v[j], inv), MAGIC), MAGIC);
+        const float qf = fminf(fmaxf(__fadd_rn(r, zf), 0.0f), 15.0f);
+        dz[j] = __fsub_rn(qf, zf);                                           // q - z in [-15, 15]
+    }
+    uint32_t pk[2];
+    if constexpr (F8) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint16_t p01, p23;      // the second source operand lands in the low byte
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(p01) : "f"(dz[4 * h + 1]), "f"(dz[4 * h]));
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(p23) : "f"(dz[4 * h + 3]), "f"(dz[4 * h + 2]));
+            pk[h] = (uint32_t) p01 | ((uint32_t) p23 << 16);
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(__fmaf_rn(dz[4 * h + j], (float) RQ_ACT_SCALE, MAGIC));
+            uint32_t lo01, lo23;
+            asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo01) : "r"(w[0]), "r"(w[1]));      // {w0.b0, w1.b0, ., .}
+            asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo23) : "r"(w[2]), "r"(w[3]));
+            asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(pk[h]) : "r"(lo01), "r"(lo23));     // {lo01.b0, lo01.b1, lo23.b0, lo23.b1}
+        }
     }
     return make_uint2(pk[0], pk[1]);
 }
-// what the multiplier word holds: m_g, or for the fp8 path the f32 bits of m_g / 16 (exact)
+// what the multiplier word holds: m_g as an integer, or for the fp8 path the f32 bits of m_g / 16 (exact)
 template <bool F8>
-__device__ __forceinline__ int multiplier_word(int mi) {
-    return F8 ? __float_as_int(__fmul_rn((float) mi, 0.0625f)) : mi;
+__device__ __forceinline__ int multiplier_word(float mf) {
+    return F8 ? __float_as_int(__fmul_rn(mf, 0.0625f)) : (int) mf;
 }
 
 // maximum over the CTA of a per-thread value >= 0: warp shuffles, one shared-memory round, result in every thread of
