@@ -147,6 +147,8 @@ __global__ void __launch_bounds__((CONSUMERS + 1) * 32) rq_gemv_mma_kernel(const
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                                  :: "r"(smem_u32(ring + (size_t) s * ST_BYTES)), "l"(src + (size_t) st * ST_BYTES), "r"(bytes), "r"(bar) : "memory");
                     ++issued;
+                    // (asking L2 for the stream behind the ring at this point -- per line or with bulk prefetches -- made the pass
+                    // slower: 3.86 against 3.72 ms with 128 KB per CTA)
                     if (issued == STAGES) read_format();      // the ring is full: nothing to issue until the consumers run
                 }
             }
