@@ -438,17 +438,16 @@ def run_ours(args):
             # would take; identical bits by construction), then every rank multiplies all tokens by its own rows
             share = world > 1 and dst is not None and M % world == 0 and not args.replicated_quantizer
             if share:
-                a8v, mshv, uv = rq.workspace_views(ws, K, M, 64)
-                t0, t1 = rank * (M // world), (rank + 1) * (M // world)
-                slabs = [(a8v, torch.empty_like(a8v[t0:t1])), (mshv, torch.empty_like(mshv[t0:t1])), (uv, torch.empty_like(uv[t0:t1]))]
+                from ruquant_b200 import shard
+                regions = list(rq.workspace_views(ws, K, M, 64))
+                t0, t1 = shard.token_range(M, rank, world)
+                scratch = [torch.empty_like(r[t0:t1]) for r in regions]
                 fmt = rq.act_format(w, M)
 
             def node():
                 if share:
                     rq.quantize_rows(x[t0:t1], M, t0, w.n_rot, 1.0, 64, fmt, ws, stream=stream)
-                    for region, tmp in slabs:
-                        tmp.copy_(region[t0:t1])
-                        dist.all_gather_into_tensor(region.view(-1), tmp.view(-1))
+                    shard.exchange_token_ranges(regions, rank, scratch=scratch)
                     rq.mul_mat_push([w], None, dst, [N], act_group=64, workspace=ws, stream=stream, M=M)
                     rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
                     return

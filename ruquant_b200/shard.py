@@ -12,8 +12,15 @@ Two ways, both from the reference:
   is taken in rank order on every rank, so all ranks hold the same bits and a CPU restatement can reproduce them
   (a ring all-reduce would not promise an order).
 
+* tokens (M), for wide inputs on row-split ranks: the rotate + quantize step is per token, so rank r does tokens
+  [r*M/g, (r+1)*M/g) (rq_w4a4_quantize_rows) and the ranks exchange the results -- one byte per input, a multiplier per
+  group, a unit per token: a quarter of what x itself takes -- before each multiplies all tokens by its own rows.
+  Identical bits by construction.
+
 torch.distributed is used for the exchange only; the functions work with any backend (gloo on CPU tensors in the
-tests, NCCL on CUDA tensors on the GPUs).
+tests, NCCL on CUDA tensors on the GPUs).  On the GPUs the outputs of row-split ranks and the partials of column-split
+ranks can also travel without a collective: rq_w4a4_mul_mat_push / rq_rank_barrier / rq_w4a4_sum_partials over
+peer-mapped buffers (ruquant_b200.mul_mat_push, rank_barrier, sum_partials).
 """
 BLOCK_CODES, BLOCK_BYTES = 256, 144
 
@@ -62,3 +69,25 @@ def sum_partials(y_partial, group=None):
     for p in parts[1:]:
         total += p
     return total
+
+
+def token_range(M, rank, world):
+    """Tokens [lo, hi) rank `rank` rotates and quantizes when the ranks share that work."""
+    if M % world:
+        raise ValueError("M = %d does not split over %d ranks" % (M, world))
+    n = M // world
+    return rank * n, (rank + 1) * n
+
+
+def exchange_token_ranges(regions, rank, group=None, scratch=None):
+    """regions: tensors whose first dimension is the token (the workspace's codes [M, K], multipliers [M, K/G], units
+    [M]), each holding this rank's token range already; on return every rank holds all ranges.  In place: the own range
+    is copied out first (to `scratch[i]` if given, a tensor shaped like the range), then all-gathered into the region."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    for i, region in enumerate(regions):
+        lo, hi = token_range(region.shape[0], rank, world)
+        tmp = scratch[i] if scratch is not None else torch.empty_like(region[lo:hi])
+        tmp.copy_(region[lo:hi])
+        dist.all_gather_into_tensor(region.view(-1), tmp.view(-1), group=group)

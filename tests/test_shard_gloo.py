@@ -67,7 +67,37 @@ def _cols_worker(rank, world, tcp, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_rows_worker, _cols_worker], ids=["rows", "columns"])
+def _tokens_worker(rank, world, tcp, out):
+    """Ranks sharing the quantizer: each quantizes its range of tokens (the oracle stands in for rq_w4a4_quantize_rows),
+    the ranges are exchanged in place, every rank then holds what quantizing all tokens gives."""
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % tcp, rank=rank, world_size=world)
+    port = oracle.Port()
+    Mt = 6
+    x = inputs.outlier_activations(Mt, K, 8300)
+    whole = port.quantize_act(x, 0.9, 64, K)                              # [Mt, K/256*144] activation blocks
+    u_all, m_all, z_all, q_all = oracle.act_fields(whole, 64)
+    lo, hi = shard.token_range(Mt, rank, world)
+    mine = port.quantize_act(np.ascontiguousarray(x[lo:hi]), 0.9, 64, K)
+    u, m, z, q = oracle.act_fields(mine, 64)
+    codes = torch.zeros((Mt, K), dtype=torch.int8)
+    mult = torch.zeros((Mt, K // 64), dtype=torch.int32)
+    unit = torch.zeros((Mt,), dtype=torch.float32)
+    codes[lo:hi] = torch.from_numpy((q - np.repeat(z, 64, axis=1)).astype(np.int8))
+    mult[lo:hi] = torch.from_numpy(m.astype(np.int32))
+    unit[lo:hi] = torch.from_numpy(u)
+    shard.exchange_token_ranges([codes, mult, unit], rank)
+    ok = bool((codes.numpy() == (q_all - np.repeat(z_all, 64, axis=1))).all() and (mult.numpy() == m_all).all() and
+              (unit.numpy().view(np.uint32) == u_all.view(np.uint32)).all())
+    flags = [None] * world
+    dist.all_gather_object(flags, ok)
+    if rank == 0:
+        with open(out, "w") as f:
+            f.write("ok" if all(flags) else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_rows_worker, _cols_worker, _tokens_worker], ids=["rows", "columns", "tokens"])
 def test_two_ranks(tmp_path, worker):
     out = str(tmp_path / "result")
     mp.spawn(worker, args=(2, _free_port(), out), nprocs=2, join=True)
