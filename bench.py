@@ -436,7 +436,11 @@ def run_ours(args):
             # N > 1: the ranks share the rotate+quantize work too -- rank r does tokens [r*M/g, (r+1)*M/g), the ranks exchange
             # the one-byte codes, group multipliers and token units (M*K bytes and a little, a quarter of what x itself
             # would take; identical bits by construction), then every rank multiplies all tokens by its own rows
-            share = world > 1 and dst is not None and M % world == 0 and not args.replicated_quantizer
+            # (worth it where the rotation is expensive: at K = 5120 the replicated quantizer takes 74 us and the exchange --
+            # three copies and three NCCL all-gathers -- costs more than the 55 us it saves on 4 GPUs: 0.591 against 0.539 ms;
+            # at K = 17408, 315 us replicated, sharing wins: 0.654 against 0.707 ms)
+            share = (world > 1 and dst is not None and M % world == 0 and not args.replicated_quantizer and
+                     K * max(w.desc.had_p, 1) >= 400000)
             if share:
                 from ruquant_b200 import shard
                 regions = list(rq.workspace_views(ws, K, M, 64))
@@ -501,8 +505,7 @@ def run_ours(args):
                    "ms_node_compute_only": ms_local, "tops_node_compute_only": ops / (ms_local * 1e-3) / 1e12,
                    "nvlink_bytes_out_per_rank": (world - 1) * M * nl * 4,
                    "quantizer": "shared: each rank quantizes M/%d tokens, codes exchanged (%d bytes in per rank)" % (
-                       world, (world - 1) * (M // world) * (K + 4 * (K // 64) + 4)) if (world > 1 and dst is not None and M % world == 0 and
-                                                                                      not args.replicated_quantizer) else "replicated on every rank",
+                       world, (world - 1) * (M // world) * (K + 4 * (K // 64) + 4)) if share else "replicated on every rank",
                    "tops_gemm_kernel": tops_gemm, "ms_gemm_kernel": ms_gemm,
                    "int8_dense_peak_nominal_tops": 4500.0 * world,
                    "frac_of_nominal_int8_peak": ops / (ms_node * 1e-3) / 1e12 / (4500.0 * world),
