@@ -597,6 +597,82 @@ def run_ours(args):
                          "frac_of_nominal_int8_peak": ops_stack / (ms_stack * 1e-3) / 1e12 / (4500.0 * world),
                          "nvlink_bytes_in_per_rank_per_pass": (world - 1) * sum(Mp * (N // world) * 4 for (_k, N) in mats),
                          "exchange": "none" if world == 1 else "ncclAllGather per matmul output"}
+        # ---- the same pass in the reference's own tensor-parallel arrangement (src/convert.rs:120-128, mxpatch:5293-5374):
+        # q/k/v and gate/up stay split along N and nothing is gathered (their consumers are sharded the same way), o and
+        # down are split along K (block-diagonal rotation): every rank multiplies its slice of x by its block columns and
+        # the partial outputs are added in rank order over peer-mapped buffers.  A K slice that is not a whole number of
+        # blocks with a factorable length (down on 8 ranks: 2176 inputs) stays split along N with its all-gather.
+        if world > 1 and push is not None:
+            symm = push["symm"]
+            two_shot = world > 2
+            ksplit = {}
+            for name in ("o", "down"):
+                K, N = LAYER_DIMS[name]
+                ks = K // world
+                if K % world or ks % 256 or rq.hadamard_factor(ks) is None:
+                    continue
+                g = torch.Generator(device=dev)
+                g.manual_seed(9000 + rank + 16 * len(ksplit))
+                part = symm.empty(Mp * N, dtype=torch.float32, device=dev)
+                yk = symm.empty(Mp * N, dtype=torch.float32, device=dev)
+                ksplit[name] = {"ks": ks, "N": N, "x": torch.randn((Mp, ks), generator=g, device=dev, dtype=torch.float32),
+                                "ws": rq.new_workspace(ks, Mp, dev), "part": part, "y": yk,
+                                "pptrs": [int(p) for p in symm.rendezvous(part, dist.group.WORLD).buffer_ptrs],
+                                "yptrs": [int(p) for p in symm.rendezvous(yk, dist.group.WORLD).buffer_ptrs], "w": []}
+                for layer in range(L):
+                    blocks = synth.random_weights(N, ks, rq.TYPE_W4A4H, seed=8_000_000 + 100 * layer + rank, device=dev)
+                    wk_ = rq.Weight(blocks.view(-1), rq.TYPE_W4A4H, ks, N=N, layouts=rq.PREPACK_PREFILL)
+                    wk_.blocks = None
+                    del blocks
+                    ksplit[name]["w"].append(wk_)
+
+            def barrier():
+                rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
+
+            def tp_pass(exchange):
+                for i, (K, _x, _ws, members, _g, _dst) in enumerate(groups):
+                    name = GROUPS[i % len(GROUPS)][0]
+                    ksp = ksplit.get(name) if len(members) == 1 else None
+                    if ksp is None:
+                        rq.mul_mat([m[2] for m in members], xs[K], out=[ys[m[0]] for m in members], clip=1.0, act_group=64,
+                                   path=rq.PATH_TC, workspace=wss[K], stream=stream)
+                        if exchange and len(members) == 1:       # o / down that could not be split along K
+                            dist.all_gather_into_tensor(yg[members[0][0]].view(-1), ys[members[0][0]].view(-1))
+                        continue
+                    N = ksp["N"]
+                    rq.mul_mat(ksp["w"][i // len(GROUPS)], ksp["x"], out=ksp["part"].view(Mp, N), clip=1.0, act_group=64,
+                               path=rq.PATH_TC, workspace=ksp["ws"], stream=stream)
+                    if not exchange:
+                        continue
+                    # o and down have partial buffers of their own and alternate: the barrier ahead of one's sum is also
+                    # the barrier after the other's, so a one-shot sum needs no second one while both are split along K
+                    barrier()
+                    rq.sum_partials(ksp["pptrs"], rank, Mp * N, ksp["yptrs"] if two_shot else
+                                    [p if r == rank else 0 for r, p in enumerate(ksp["yptrs"])], two_shot=two_shot, stream=stream)
+                    if two_shot or len(ksplit) < 2:
+                        barrier()
+
+            ms_tp = timed(lambda: tp_pass(True), 2, 1)
+            ms_tp_local = timed(lambda: tp_pass(False), 2, 1)
+            chk = []
+            for name, ksp in ksplit.items():
+                rq.device_status(ksp["ws"], ksp["ks"], Mp)
+                got = [torch.empty_like(ksp["y"]) for _ in range(world)]
+                dist.all_gather(got, ksp["y"])
+                chk.append(all(bool((c.view(torch.int32) == ksp["y"].view(torch.int32)).all().item()) for c in got))
+            n_sum = (2.0 * (world - 1) / world if two_shot else float(world - 1))
+            prefill_stack["tensor_parallel"] = {
+                "arrangement": "q/k/v, gate/up split along N, outputs left sharded; %s split along K, partial outputs added in rank "
+                               "order (%s)" % (", ".join(sorted(ksplit)) or "no tensor", "two-shot" if two_shot else "one-shot"),
+                "n_split_with_all_gather": [n for n in ("o", "down") if n not in ksplit],
+                "ms_per_pass": ms_tp, "tops": ops_stack / (ms_tp * 1e-3) / 1e12,
+                "ms_per_pass_compute_only": ms_tp_local, "tops_compute_only": ops_stack / (ms_tp_local * 1e-3) / 1e12,
+                "frac_of_nominal_int8_peak": ops_stack / (ms_tp * 1e-3) / 1e12 / (4500.0 * world),
+                "nvlink_bytes_in_per_rank_per_pass": int(L * sum(n_sum * Mp * k["N"] * 4 for k in ksplit.values())),
+                "all_ranks_bit_identical": all(chk) and int(push["status"].item()) == 0,
+                "note": "a K-split rank quantizes its slice of x with its own range, in the reference as here: the sums are not "
+                        "the one-GPU outputs (the N split's are)"}
+            del ksplit
         del xs, wss, ys, yg
 
     # ---- the reference's own tensor-parallel mode for attn_output / ffn_down: weights split along K (block-diagonal
