@@ -626,7 +626,7 @@ def run_ours(args):
                     del blocks
                     ksplit[name]["w"].append(wk_)
 
-            def barrier():
+            def ranks_meet():
                 rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
 
             def tp_pass(exchange):
@@ -646,11 +646,11 @@ def run_ours(args):
                         continue
                     # o and down have partial buffers of their own and alternate: the barrier ahead of one's sum is also
                     # the barrier after the other's, so a one-shot sum needs no second one while both are split along K
-                    barrier()
+                    ranks_meet()
                     rq.sum_partials(ksp["pptrs"], rank, Mp * N, ksp["yptrs"] if two_shot else
                                     [p if r == rank else 0 for r, p in enumerate(ksp["yptrs"])], two_shot=two_shot, stream=stream)
                     if two_shot or len(ksplit) < 2:
-                        barrier()
+                        ranks_meet()
 
             ms_tp = timed(lambda: tp_pass(True), 2, 1)
             ms_tp_local = timed(lambda: tp_pass(False), 2, 1)
