@@ -359,8 +359,12 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             RQ_CYC_REPORT(prm.status, 0x40, c_empty);
             RQ_CYC_REPORT(prm.status, 0x41, c_total);
             if (*abort_flag) {
-                // drain: every slice that was issued must land before the CTA's shared memory is given back (rank 1 of a
-                // pair cannot see its own copies complete: it gives them time, then meets rank 0 at the final barrier)
+                // drain: every slice that was issued must land before the CTA's shared memory is given back.  In a pair
+                // both CTAs' bytes complete on rank 0's barriers, so rank 0's waits cover rank 1's copies of the same
+                // slices, and rank 1 cannot leave before them: this thread of rank 0 reaches the cluster barrier at the end
+                // of the kernel only after the loop below.  Rank 1 can be at most the slice it has just issued ahead of
+                // rank 0 (both producers follow the same commits); it cannot watch a remote barrier, so it gives that one
+                // copy 100 us -- it was issued into a free slot, a second after everything else stopped.
                 if (!PAIR || leader) {
                     for (uint32_t k = it > (uint32_t) STAGES ? it - STAGES : 0; k < it; ++k) {
                         const long long t0 = clock64();
@@ -368,7 +372,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                 } else {
                     const long long t0 = clock64();
-                    while (clock64() - t0 < 2000000ll) { }
+                    while (clock64() - t0 < 200000ll) { }
                 }
             }
         }
