@@ -23,6 +23,8 @@
 // CTAs' tensor memory, each CTA stages its own 128 tokens of A and only HALF of the 256 weight rows of B (32 KB per
 // slice instead of 48 KB, six stages).  The even CTA issues the MMAs for both; its commits signal the barriers of both
 // CTAs, the odd CTA's TMA bytes and epilogue arrivals are counted on the even CTA's barriers.
+// PUSH (N-sharded ranks): warps 2 and 3 copy every finished unit from this GPU's output into the other ranks' copies
+// (peer stores), so that no folding warp ever waits for NVLink.
 // Every wait is bounded: on expiry the waiter raises a CTA-wide abort flag and a status word in global memory,
 // everyone leaves the pipeline, outstanding TMA transactions are drained and tensor memory is released.
 #include <cuda.h>
@@ -267,6 +269,7 @@ struct __align__(8) TcShared {
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
+    unsigned int units_stored;          // PUSH: epilogue warps that have stored a unit, summed over units (8 per unit)
 };
 
 // F8 = true: multipliers all 1, operands are e4m3 bytes of c and (q - z), fp8 MMA with fp32 accumulators, float fold.
@@ -301,6 +304,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // a pair's accumulator buffer is free when the 8 epilogue warps of BOTH CTAs have arrived (on rank 0's barrier)
         for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&sh.tmem_full[b]), 1); mbar_init(smem_u32(&sh.tmem_empty[b]), PAIR ? 16 : 8); }
         sh.abort_flag = 0;
+        sh.units_stored = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -441,6 +445,59 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             RQ_CYC_REPORT(prm.status, 0x44, c_mma);
             RQ_CYC_REPORT(prm.status, 0x47, c_issue);
             RQ_CYC_REPORT(prm.status, 0x48, c_commit);
+            }
+        }
+    } else if (PUSH && prm.n_more > 0) {
+        // Warps 2 and 3 carry the finished units to the other ranks.  The epilogue warps store a unit into this GPU's
+        // output only; these two warps read it back (from L2) and store it into every other rank's copy.  Peer stores
+        // drain at NVLink speed -- a quarter of a unit's fold time per destination at best -- and a warp that waits for
+        // them cannot fold: issued by the epilogue warps they added their whole duration to the kernel.
+        const int pw = warp - 2;
+        const bool fmt_ok = prm.status == nullptr || prm.status[1] == (F8 ? RQ_FMT_E4M3 : RQ_FMT_I8);
+        volatile unsigned int * stored = &sh.units_stored;
+        unsigned int k = 0;
+        for (int v = first; v < units; v += stride, ++k) {
+            bool ok = true;
+            const long long t0 = clock64();
+            while (*stored < 8u * (k + 1u)) {          // bounded, like every wait of this kernel
+                if (*abort_flag) { ok = false; break; }
+                if (clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; ok = false; break; }
+                __nanosleep(256);
+            }
+            if (!__all_sync(0xffffffffu, ok)) break;
+            __threadfence();
+            if (!fmt_ok) continue;
+            const int n_tile = v / m_units, m_unit = v - n_tile * m_units;
+            const int m_tile = PAIR ? 2 * m_unit + (int) rank : m_unit;
+            const int row0 = m_tile * BM, col = n_tile * BN + (pw * 32 + lane) * 4;      // 64 lanes x 4 columns = a unit's row
+            const int rows = prm.M - row0 < BM ? prm.M - row0 : BM;
+            if (prm.vec && col + 3 < prm.N) {
+                // four rows of loads in flight per lane (eight, with registers taken from the epilogue warps, changed
+                // nothing: 0.494 against 0.497 ms for the 4096 x 17408 node on 4 GPUs -- the peer stores set the pace, about
+                // 3.4 GB/s per SM whichever warps issue them)
+                for (int r = 0; r < rows; r += 4) {
+                    float4 q[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (r + u < rows) q[u] = __ldcg(reinterpret_cast<const float4 *>(prm.y + (size_t) (row0 + r + u) * prm.ldy + col));
+                    for (int d = 0; d < prm.n_more; ++d) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (r + u < rows) *reinterpret_cast<float4 *>(prm.y_more[d] + (size_t) (row0 + r + u) * prm.ldy + col) = q[u];
+                    }
+                }
+            } else if (col < prm.N) {
+                for (int r = 0; r < rows; ++r) {
+                    const size_t at = (size_t) (row0 + r) * prm.ldy + col;
+                    float q[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) q[u] = col + u < prm.N ? __ldcg(prm.y + at + u) : 0.0f;
+                    for (int d = 0; d < prm.n_more; ++d) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (col + u < prm.N) prm.y_more[d][at + u] = q[u];
+                    }
+                }
             }
         }
     }
@@ -632,24 +689,27 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         const float4 q = *reinterpret_cast<const float4 *>(stg + rr * 32 + ((jj ^ (rr & 7)) << 2));
                         const float o0 = __fmul_rn(q.x, sc[c][0]), o1 = __fmul_rn(q.y, sc[c][1]), o2 = __fmul_rn(q.z, sc[c][2]), o3 = __fmul_rn(q.w, sc[c][3]);
                         if (grow < prm.M) {
-                            // destination 0 is this GPU's buffer; N-sharded ranks get the same 128-byte row pieces straight
-                            // into their copies of the output while the MMAs of the next unit run
-                            for (int dd = 0; dd <= (PUSH ? prm.n_more : 0); ++dd) {
-                                float * yr = (!PUSH || dd == 0 ? prm.y : prm.y_more[dd - 1]) + (size_t) grow * prm.ldy + ncol;
-                                if (vec && ncol + 3 < prm.N) {
-                                    *reinterpret_cast<float4 *>(yr) = make_float4(o0, o1, o2, o3);
-                                } else {
-                                    if (ncol < prm.N) yr[0] = o0;
-                                    if (ncol + 1 < prm.N) yr[1] = o1;
-                                    if (ncol + 2 < prm.N) yr[2] = o2;
-                                    if (ncol + 3 < prm.N) yr[3] = o3;
-                                }
+                            // this GPU's buffer; N-sharded ranks get their copies from warps 2 and 3
+                            float * yr = prm.y + (size_t) grow * prm.ldy + ncol;
+                            if (vec && ncol + 3 < prm.N) {
+                                *reinterpret_cast<float4 *>(yr) = make_float4(o0, o1, o2, o3);
+                            } else {
+                                if (ncol < prm.N) yr[0] = o0;
+                                if (ncol + 1 < prm.N) yr[1] = o1;
+                                if (ncol + 2 < prm.N) yr[2] = o2;
+                                if (ncol + 3 < prm.N) yr[3] = o3;
                             }
                         }
                     }
                     __syncwarp();
                 }
                 }
+            }
+            if constexpr (PUSH) {
+                // the unit is in this GPU's output: let the pushing warps see it
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(&sh.units_stored, 1u);
             }
             RQ_CYC_END(c_fin);
         }
