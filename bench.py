@@ -558,7 +558,9 @@ def run_ours(args):
 
     # ---- configuration 5 at M = 4096: one pass over the whole stack (1.787e14 operations at 64 layers).  The linears are
     # not chained: every activation width has one seeded N(0,1) input, every output width one buffer.  N-sharded ranks
-    # assemble each matmul's output with an NCCL all-gather (the exchange BASELINE.json's configuration names).
+    # assemble every matmul's output on every rank: the GEMM's copy warps store each finished unit into the other ranks'
+    # gathered [M][N] buffers while the next units fold, one barrier kernel per layer (an NCCL all-gather after every
+    # matmul where the buffers cannot be mapped).
     prefill_stack = None
     if not args.no_prefill and not args.no_prefill_stack:
         Mp = PREFILL[3]
@@ -577,9 +579,25 @@ def run_ours(args):
                     if world > 1:
                         yg[N] = torch.empty((world, Mp, N // world), device=dev, dtype=torch.float32)
 
+        ygs, ygp = {}, {}       # gathered [M][N] outputs mapped into every rank, and their addresses (own buffer first)
+        if push is not None:
+            for name, _k, N in LAYER:      # one gathered buffer per tensor of the layer
+                ygs[name] = push["symm"].empty(Mp * N, dtype=torch.float32, device=dev)
+                hdl = push["symm"].rendezvous(ygs[name], dist.group.WORLD)
+                ygp[name] = [int(hdl.buffer_ptrs[r]) for r in push["order"]]
+            torch.cuda.synchronize()
+            dist.barrier()
+
         def stack_pass(gather):
-            for K, _x, _ws, members, _g, _dst in groups:
+            for i, (K, _x, _ws, members, _g, _dst) in enumerate(groups):
                 weights = [m[2] for m in members]
+                if gather and push is not None:
+                    names = GROUPS[i % len(GROUPS)]
+                    rq.mul_mat_push(weights, xs[K], [[ygp[nm][d] + 4 * rank * m[1] for nm, m in zip(names, members)] for d in range(world)],
+                                    [m[0] for m in members], clip=1.0, act_group=64, workspace=wss[K], stream=stream)
+                    if i % len(GROUPS) == len(GROUPS) - 1:
+                        rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
+                    continue
                 outs = [ys[m[0]] for m in members]
                 rq.mul_mat(weights, xs[K], out=outs, clip=1.0, act_group=64, path=rq.PATH_TC, workspace=wss[K], stream=stream)
                 if gather and world > 1:
@@ -591,12 +609,27 @@ def run_ours(args):
         ms_stack_local = timed(lambda: stack_pass(False), 2, 1) if world > 1 else ms_stack
         for K in wss:
             rq.device_status(wss[K], K, Mp)
+        stack_check = None
+        if push is not None:
+            # what the last down projection left in every rank's gathered buffer against an NCCL all-gather of the slices
+            Nd = LAYER_DIMS["down"][1]
+            nl = Nd // world
+            mine = ygs["down"].view(Mp, Nd)[:, rank * nl:(rank + 1) * nl].contiguous()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            same = bool((torch.cat(parts, dim=1).view(torch.int32) == ygs["down"].view(Mp, Nd).view(torch.int32)).all().item())
+            flag = torch.tensor([1 if same and int(push["status"].item()) == 0 else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            stack_check = "equal" if int(flag.item()) == 1 else "FAILED"
         prefill_stack = {"workload": "%d-layer stack, M=%d prefill, 7 matmuls per layer (%.4g operations per pass)" % (L, Mp, ops_stack),
                          "ms_per_pass": ms_stack, "tops": ops_stack / (ms_stack * 1e-3) / 1e12,
                          "ms_per_pass_compute_only": ms_stack_local, "tops_compute_only": ops_stack / (ms_stack_local * 1e-3) / 1e12,
                          "frac_of_nominal_int8_peak": ops_stack / (ms_stack * 1e-3) / 1e12 / (4500.0 * world),
                          "nvlink_bytes_in_per_rank_per_pass": (world - 1) * sum(Mp * (N // world) * 4 for (_k, N) in mats),
-                         "exchange": "none" if world == 1 else "ncclAllGather per matmul output"}
+                         "exchange": "none" if world == 1 else ("outputs stored into every rank's gathered buffers by the GEMM's copy "
+                                                                "warps, one barrier kernel per layer" if push is not None else
+                                                                "ncclAllGather per matmul output"),
+                         "pushed_vs_all_gather": stack_check}
         # ---- the same pass in the reference's own tensor-parallel arrangement (src/convert.rs:120-128, mxpatch:5293-5374):
         # q/k/v and gate/up stay split along N and nothing is gathered (their consumers are sharded the same way), o and
         # down are split along K (block-diagonal rotation): every rank multiplies its slice of x by its block columns and
@@ -673,7 +706,7 @@ def run_ours(args):
                 "note": "a K-split rank quantizes its slice of x with its own range, in the reference as here: the sums are not "
                         "the one-GPU outputs (the N split's are)"}
             del ksplit
-        del xs, wss, ys, yg
+        del xs, wss, ys, yg, ygs
 
     # ---- the reference's own tensor-parallel mode for attn_output / ffn_down: weights split along K (block-diagonal
     # rotation, `--rot-blocks`), every rank multiplies its slice of x by its block columns, the partial outputs are added in
