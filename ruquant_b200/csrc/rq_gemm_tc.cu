@@ -456,7 +456,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const bool fmt_ok = prm.status == nullptr || prm.status[1] == (F8 ? RQ_FMT_E4M3 : RQ_FMT_I8);
         volatile unsigned int * stored = &sh.units_stored;
         unsigned int k = 0;
-        for (int v = first; v < units; v += stride, ++k) {
+        // (a wrong activation format: the epilogue warps store nothing and count nothing, so there is nothing to wait for)
+        for (int v = first; v < units && fmt_ok; v += stride, ++k) {
             bool ok = true;
             const long long t0 = clock64();
             while (*stored < 8u * (k + 1u)) {          // bounded, like every wait of this kernel
@@ -466,7 +467,6 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             if (!__all_sync(0xffffffffu, ok)) break;
             __threadfence();
-            if (!fmt_ok) continue;
             const int n_tile = v / m_units, m_unit = v - n_tile * m_units;
             const int m_tile = PAIR ? 2 * m_unit + (int) rank : m_unit;
             const int row0 = m_tile * BM, col = n_tile * BN + (pw * 32 + lane) * 4;      // 64 lanes x 4 columns = a unit's row

@@ -125,6 +125,29 @@ def test_push_from_every_tensor_core_variant(rq, port, wgroup, M):
     assert float(b[0].item()) == -1.0
 
 
+def test_push_refuses_the_wrong_activation_format_at_once(rq, port):
+    """Tokens quantized for the integer GEMV handed to the pushing tensor-core kernel: status -7, nothing stored in either
+    destination, and no warp of the kernel sits out a bounded wait for the stores that never come."""
+    import time
+    K, N, M = 1536, 328, 200
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9830), 45)
+    w = rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    x = dev(inputs.outlier_activations(M, K, 9831))
+    ws = rq.new_workspace(K, M)
+    rq.quantize_rows(x, M, 0, w.n_rot, 1.0, 64, rq.FMT_I8, ws)
+    bufs = [torch.full((M, N), 7.0, dtype=torch.float32, device="cuda") for _ in range(2)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rq.mul_mat_push([w], None, [[b.data_ptr()] for b in bufs], [N], act_group=64, workspace=ws, M=M)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5
+    with pytest.raises(rq.RqError) as e:
+        rq.device_status(ws, K, M)
+    assert e.value.status == -7
+    for b in bufs:
+        assert (b == 7.0).all()
+
+
 @pytest.mark.parametrize("M", [12, 200])
 def test_token_ranges_quantized_apart_multiply_like_the_whole(rq, port, M):
     """Ranks that share the quantizer's work: token ranges rotated and quantized by separate rq_w4a4_quantize_rows calls
