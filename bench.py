@@ -436,23 +436,28 @@ def run_ours(args):
             # N > 1: the ranks share the rotate+quantize work too -- rank r does tokens [r*M/g, (r+1)*M/g), the ranks exchange
             # the one-byte codes, group multipliers and token units (M*K bytes and a little, a quarter of what x itself
             # would take; identical bits by construction), then every rank multiplies all tokens by its own rows
-            # (worth it where the rotation is expensive: at K = 5120 the replicated quantizer takes 74 us and the exchange --
-            # three copies and three NCCL all-gathers -- costs more than the 55 us it saves on 4 GPUs: 0.591 against 0.539 ms;
-            # at K = 17408, 315 us replicated, sharing wins: 0.654 against 0.707 ms)
+            # (worth it where the rotation is expensive: at K = 17408, 315 us replicated, the node takes 0.566 ms shared against
+            # 0.707 replicated on 4 GPUs; at K = 5120, 74 us replicated, 0.493 against 0.497)
             share = (world > 1 and dst is not None and M % world == 0 and not args.replicated_quantizer and
-                     K * max(w.desc.had_p, 1) >= 400000)
+                     K * max(w.desc.had_p, 1) >= args.share_threshold)
             if share:
+                # the workspace lives in memory mapped into every rank: one copy kernel carries this rank's rows to the others
                 from ruquant_b200 import shard
-                regions = list(rq.workspace_views(ws, K, M, 64))
+                ws = rq.init_workspace(push["symm"].empty(rq.workspace_bytes(K, M), dtype=torch.uint8, device=dev), K, M)
+                ws_hdl = push["symm"].rendezvous(ws, dist.group.WORLD)
+                ws_ptrs = [int(p) for p in ws_hdl.buffer_ptrs]
                 t0, t1 = shard.token_range(M, rank, world)
-                scratch = [torch.empty_like(r[t0:t1]) for r in regions]
                 fmt = rq.act_format(w, M)
+                torch.cuda.synchronize()
+                dist.barrier()
 
             def node():
                 if share:
                     rq.quantize_rows(x[t0:t1], M, t0, w.n_rot, 1.0, 64, fmt, ws, stream=stream)
-                    shard.exchange_token_ranges(regions, rank, scratch=scratch)
+                    rq.share_rows(ws_ptrs, rank, ws.numel(), K, M, 64, t0, t1 - t0, stream=stream)
+                    rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
                     rq.mul_mat_push([w], None, dst, [N], act_group=64, workspace=ws, stream=stream, M=M)
+                    # (this barrier also stands between the ranks' reads of the workspaces and the next step's rows)
                     rq.rank_barrier(push["flag_ptrs"], rank, push["epoch"], push["status"], stream=stream)
                     return
                 if dst is not None:
@@ -959,6 +964,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-prefill-stack", action="store_true", help="skip the M = 4096 pass over the whole stack")
     ap.add_argument("--replicated-quantizer", action="store_true", help="N > 1 prefill: every rank quantizes all tokens (no exchange of codes)")
+    ap.add_argument("--share-threshold", type=int, default=400000,
+                    help="N > 1 prefill: ranks share the quantizer where K times the Paley order reaches this")
     ap.add_argument("--no-perf-shapes", action="store_true", help="skip the reference's own performance shapes")
     ap.add_argument("--single", default="", help="K,N,M[,type]: time one shape instead of the stack")
     ap.add_argument("--wquant", default="", help="K,N[,type[,wgroup]]: time the GPU weight quantizer beside the reference's CPU code")

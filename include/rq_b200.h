@@ -160,6 +160,15 @@ int rq_w4a4_quantize_rows(const float * x_rows_dev, int64_t ldx, int64_t M_total
                           int64_t n_rot, float clip, int act_group, int act_format, void * workspace_dev,
                           size_t workspace_bytes, void * stream);
 
+/* The exchange for ranks whose workspaces are mapped into one another (cudaIpc / symmetric memory): one copy kernel
+ * stores rows [first, first + count) of this rank's three regions into the same rows of every other rank's workspace.
+ * workspace_of_rank[r]: rank r's workspace as mapped on this device, all laid out for the same K and M_total;
+ * workspace_of_rank[rank] is the source.  An rq_rank_barrier after the call makes every rank's rows visible everywhere;
+ * a workspace must not be quantized into again before the ranks that read it have passed a later barrier.  The reference
+ * has no counterpart: its ranks each rotate and quantize every token.  Capture-safe. */
+int rq_w4a4_share_rows(void * const * workspace_of_rank, int rank, int n_ranks, size_t workspace_bytes, int64_t K,
+                       int64_t M_total, int act_group, int64_t first, int64_t count, void * stream);
+
 /* The activation format (RQ_FMT_*) the contraction of these weights at M tokens wants -- what rq_w4a4_mul_mat passes
  * to the quantizer itself; for callers that run rq_w4a4_quantize and rq_w4a4_mul_mat_quantized separately.
  * Negative rq_status on a request that cannot be served (missing layout, weights that need different formats). */

@@ -24,6 +24,7 @@ EXPORTS = [
     "rq_w4a4_mul_mat_static", "rq_w4a4_mul_mat_quantized_n", "rq_w4a4_act_format",
     "rq_w4a4_quantize_weights", "rq_w4a4_quantize_weights_scratch_bytes", "rq_w4a4_mul_mat_push", "rq_rank_barrier",
     "rq_w4a4_workspace_init", "rq_w4a4_tc_nofold_probe", "rq_w4a4_sum_partials", "rq_w4a4_quantize_rows",
+    "rq_w4a4_share_rows",
 ]
 
 
@@ -77,6 +78,7 @@ def lib():
         L.rq_w4a4_quantize.argtypes = [vp, i64, i64, i64, i64, f32, i32, i32, vp, sz, vp]
         L.rq_w4a4_act_format.argtypes = [ctypes.POINTER(pd), i32, i64, i32]
         L.rq_w4a4_quantize_rows.argtypes = [vp, i64, i64, i64, i64, i64, i64, f32, i32, i32, vp, sz, vp]
+        L.rq_w4a4_share_rows.argtypes = [vp, i32, i32, sz, i64, i64, i32, i64, i64, vp]
         L.rq_w4a4_mul_mat_push.argtypes = [ctypes.POINTER(pd), i32, vp, i64, i64, ctypes.POINTER(vp), i32, ctypes.POINTER(i64), f32,
                                            i32, vp, sz, vp]
         L.rq_rank_barrier.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vp, vp]
@@ -154,15 +156,21 @@ def workspace_bytes(K, M):
     return lib().rq_w4a4_workspace_bytes(K, M)
 
 
-def new_workspace(K, M, device="cuda"):
-    """A workspace for M tokens of width K with its status block zeroed (the error word in it is sticky).  Waits for
-    the zeroing to finish, so that the workspace may be used on any stream afterwards."""
+def init_workspace(ws, K, M):
+    """Zero the status block of a workspace the caller allocated (uint8 CUDA tensor of workspace_bytes(K, M), e.g. in
+    memory mapped into other ranks); waits for the zeroing, so that the workspace may be used on any stream afterwards."""
     import torch
-    ws = torch.empty(workspace_bytes(K, M), dtype=torch.uint8, device=device)
     with torch.cuda.device(ws.device):
         _check(lib().rq_w4a4_workspace_init(ws.data_ptr(), K, M, _stream_ptr()), "rq_w4a4_workspace_init")
         torch.cuda.current_stream().synchronize()
     return ws
+
+
+def new_workspace(K, M, device="cuda"):
+    """A workspace for M tokens of width K with its status block zeroed (the error word in it is sticky).  Waits for
+    the zeroing to finish, so that the workspace may be used on any stream afterwards."""
+    import torch
+    return init_workspace(torch.empty(workspace_bytes(K, M), dtype=torch.uint8, device=device), K, M)
 
 
 def workspace_views(ws, K, M, group):
@@ -263,6 +271,15 @@ def rank_barrier(flag_ptrs, rank, epoch, status=None, stream=None):
     arr = (ctypes.c_void_p * n)(*flag_ptrs)
     _check(lib().rq_rank_barrier(arr, rank, n, epoch.data_ptr(), status.data_ptr() if status is not None else None,
                                  _stream_ptr(stream)), "rq_rank_barrier")
+
+
+def share_rows(workspace_ptrs, rank, workspace_bytes_, K, M_total, group, first, count, stream=None):
+    """Ranks that share the quantizer: rows first .. first+count of this rank's workspace (codes, multipliers, units) into
+    the same rows of every other rank's.  workspace_ptrs[r]: rank r's workspace as mapped on this device."""
+    n = len(workspace_ptrs)
+    arr = (ctypes.c_void_p * n)(*workspace_ptrs)
+    _check(lib().rq_w4a4_share_rows(arr, rank, n, workspace_bytes_, K, M_total, group, first, count, _stream_ptr(stream)),
+           "rq_w4a4_share_rows")
 
 
 def sum_partials(partial_ptrs, rank, count, y_ptrs, two_shot=False, stream=None):

@@ -531,6 +531,28 @@ extern "C" __attribute__((visibility("default"))) int rq_w4a4_sum_partials(const
     return RQ_OK;
 }
 
+extern "C" __attribute__((visibility("default"))) int rq_w4a4_share_rows(void * const * workspace_of_rank, int rank, int n_ranks,
+                                                                       size_t workspace_bytes, int64_t K, int64_t M_total, int act_group,
+                                                                       int64_t first, int64_t count, void * stream) {
+    if (workspace_of_rank == nullptr || n_ranks < 1 || n_ranks > RQ_MAX_RANKS || rank < 0 || rank >= n_ranks) return RQ_ERR_ARG;
+    if (K <= 0 || K % RQ_BLOCK_CODES != 0 || K > RQ_MAX_K || M_total < 1) return RQ_ERR_SHAPE;
+    if (act_group != 64 && act_group != 128 && act_group != 256) return RQ_ERR_ARG;
+    if (first < 0 || count < 1 || first + count > M_total) return RQ_ERR_SHAPE;
+    const rq_ws_layout l = rq_ws(K, M_total);
+    if (workspace_bytes < l.bytes) return RQ_ERR_WORKSPACE;
+    void * dst[RQ_MAX_RANKS - 1];
+    int n_dst = 0;
+    for (int r = 0; r < n_ranks; ++r) {
+        if (workspace_of_rank[r] == nullptr || (reinterpret_cast<uintptr_t>(workspace_of_rank[r]) & 15) != 0) return RQ_ERR_ARG;
+        if (r != rank) dst[n_dst++] = workspace_of_rank[r];
+    }
+    const uint64_t n_ag = (uint64_t) (K / act_group);
+    const uint64_t off[3] = { l.off_a8 + (uint64_t) first * (uint64_t) K, l.off_msh + (uint64_t) first * n_ag * 4, l.off_u + (uint64_t) first * 4 };
+    const uint64_t bytes[3] = { (uint64_t) count * (uint64_t) K, (uint64_t) count * n_ag * 4, (uint64_t) count * 4 };
+    RQ_CUDA(rq_launch_share_rows(workspace_of_rank[rank], dst, n_dst, off, bytes, (cudaStream_t) stream));
+    return RQ_OK;
+}
+
 extern "C" __attribute__((visibility("default"))) int rq_w4a4_workspace_init(void * workspace_dev, int64_t K, int64_t M, void * stream) {
     if (workspace_dev == nullptr) return RQ_ERR_ARG;
     if (K <= 0 || K % RQ_BLOCK_CODES != 0 || M < 1) return RQ_ERR_SHAPE;

@@ -155,6 +155,8 @@ cudaError_t rq_launch_rank_barrier(uint32_t * const * flags_of_rank, int rank, i
 // rank-ordered sum of the ranks' partial outputs over elements [lo, hi), stored into n_out destinations (rq_rank.cu)
 cudaError_t rq_launch_partial_sum(const float * const * partials, int n_ranks, int64_t lo, int64_t hi, float * const * outs, int n_out,
                                   cudaStream_t stream);
+cudaError_t rq_launch_share_rows(const void * src, void * const * dst, int n_dst, const uint64_t * off, const uint64_t * bytes,
+                                 cudaStream_t stream);
 // weight quantizer: scale search + pack of already-rotated rows (rq_wquant.cu)
 cudaError_t rq_launch_wquant(const float * x, int64_t ldx, int64_t n_rows, int64_t K, int wgroup, int pad0, float * sg,
                              rq_block * out, cudaStream_t stream);

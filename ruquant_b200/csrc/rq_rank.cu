@@ -77,7 +77,60 @@ __global__ void __launch_bounds__(256) rq_partial_sum_kernel(const PartialSumPar
     }
 }
 
+// Ranks that share the quantizer: three byte ranges of this rank's workspace (codes, multipliers, units of its token
+// range) go to the same offsets of every other rank's workspace.  16-byte pieces where a range allows them, four loads
+// in flight per thread; 4-byte words otherwise (every range is a whole number of them).
+struct ShareRowsParams {
+    const uint8_t * src;
+    uint8_t * dst[RQ_MAX_RANKS - 1];
+    uint64_t off[3], bytes[3];
+    int n_dst;
+};
+
+__global__ void __launch_bounds__(256) rq_share_rows_kernel(const ShareRowsParams prm) {
+    const uint64_t tid = (uint64_t) blockIdx.x * blockDim.x + threadIdx.x, nthr = (uint64_t) gridDim.x * blockDim.x;
+    for (int seg = 0; seg < 3; ++seg) {
+        const uint64_t off = prm.off[seg], bytes = prm.bytes[seg];
+        if (((off | bytes) & 15) == 0) {
+            const uint64_t n = bytes >> 4;
+            for (uint64_t i = tid; i < n; i += 4 * nthr) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (i + u * nthr < n) v[u] = __ldcg(reinterpret_cast<const uint4 *>(prm.src + off) + i + u * nthr);
+                for (int d = 0; d < prm.n_dst; ++d) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (i + u * nthr < n) reinterpret_cast<uint4 *>(prm.dst[d] + off)[i + u * nthr] = v[u];
+                }
+            }
+        } else {
+            const uint64_t n = bytes >> 2;
+            for (uint64_t i = tid; i < n; i += nthr) {
+                const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>(prm.src + off) + i);
+                for (int d = 0; d < prm.n_dst; ++d) reinterpret_cast<uint32_t *>(prm.dst[d] + off)[i] = v;
+            }
+        }
+    }
+}
+
 }  // namespace
+
+cudaError_t rq_launch_share_rows(const void * src, void * const * dst, int n_dst, const uint64_t * off, const uint64_t * bytes,
+                                 cudaStream_t stream) {
+    ShareRowsParams prm = {};
+    prm.src = static_cast<const uint8_t *>(src);
+    for (int d = 0; d < n_dst; ++d) prm.dst[d] = static_cast<uint8_t *>(dst[d]);
+    uint64_t total = 0;
+    for (int i = 0; i < 3; ++i) { prm.off[i] = off[i]; prm.bytes[i] = bytes[i]; total += bytes[i]; }
+    prm.n_dst = n_dst;
+    if (n_dst < 1 || total == 0) return cudaSuccess;
+    uint64_t blocks = (total / 64 + 255) / 256;       // 64 bytes per thread and sweep
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    rq_share_rows_kernel<<<(unsigned) blocks, 256, 0, stream>>>(prm);
+    return cudaGetLastError();
+}
 
 cudaError_t rq_launch_partial_sum(const float * const * partials, int n_ranks, int64_t lo, int64_t hi, float * const * outs, int n_out,
                                   cudaStream_t stream) {

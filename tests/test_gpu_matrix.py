@@ -173,3 +173,37 @@ def test_token_ranges_quantized_apart_multiply_like_the_whole(rq, port, M):
     rq.device_status(ws, K, M)
     for b in bufs:
         assert_bits(b.cpu().numpy(), want, "ranges pushed, M=%d" % M)
+
+
+@pytest.mark.parametrize("group", [64, 256])
+def test_shared_rows_make_every_workspace_whole(rq, port, group):
+    """rq_w4a4_share_rows between three workspaces on one GPU standing for three ranks: each quantizes its own range of
+    tokens, copies it into the others, and every workspace must then equal, byte for byte in all three regions, the one a
+    single quantizer call fills -- and multiply like it."""
+    K, N, M = 5120, 192, 70
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9870), 45)
+    w = rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    x = inputs.outlier_activations(M, K, 9871)
+    xd = dev(x)
+    fmt = rq.act_format(w, M)
+    whole = rq.new_workspace(K, M)
+    rq.quantize_rows(xd, M, 0, w.n_rot, 1.0, group, fmt, whole)
+    cuts = [0, 23, 24, M]                       # ragged ranges, one of a single token
+    wss = [rq.new_workspace(K, M) for _ in range(3)]
+    for ws in wss:
+        ws[:ws.numel() - 256].fill_(0xA5)       # what a range does not write must come from its owner
+    ptrs = [ws.data_ptr() for ws in wss]
+    for r in range(3):
+        rq.quantize_rows(xd[cuts[r]:cuts[r + 1]], M, cuts[r], w.n_rot, 1.0, group, fmt, wss[r])
+    for r in range(3):
+        rq.share_rows(ptrs, r, wss[r].numel(), K, M, group, cuts[r], cuts[r + 1] - cuts[r])
+    torch.cuda.synchronize()
+    want_regions = rq.workspace_views(whole, K, M, group)
+    for r in range(3):
+        for got, want, name in zip(rq.workspace_views(wss[r], K, M, group), want_regions, ("codes", "multipliers", "units")):
+            assert torch.equal(got.view(torch.uint8), want.view(torch.uint8)), "%s of workspace %d" % (name, r)
+    want = port.mul_mat(wb, 45, K, x, group=group)
+    y = rq.mul_mat_quantized(w, M, wss[2], act_group=group)
+    torch.cuda.synchronize()
+    assert_bits(y.cpu().numpy(), want, "shared rows, group=%d" % group)
+
