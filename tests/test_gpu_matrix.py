@@ -207,3 +207,23 @@ def test_shared_rows_make_every_workspace_whole(rq, port, group):
     torch.cuda.synchronize()
     assert_bits(y.cpu().numpy(), want, "shared rows, group=%d" % group)
 
+
+@pytest.mark.parametrize("M", [5, 300])
+def test_push_of_a_shard_narrower_than_a_unit(rq, port, M):
+    """An eighth of a 1024-row tensor: 128 weight rows, half a 256-row unit of the tensor-core kernel, pushed into columns
+    384..511 of two gathered [M][1024] outputs; nothing outside those columns may change."""
+    K, N = 5120, 128
+    wb = port.quantize_weights(inputs.normal_weights(N, K, 9880), 45)
+    w = rq.Weight(dev(wb).view(-1), 45, K, N=N)
+    x = inputs.outlier_activations(M, K, 9881 + M)
+    full = [torch.full((M, 1024), -1.0, dtype=torch.float32, device="cuda") for _ in range(2)]
+    ws = rq.new_workspace(K, M)
+    rq.mul_mat_push([w], dev(x), [[f.data_ptr() + 4 * 384] for f in full], [1024], workspace=ws)
+    torch.cuda.synchronize()
+    rq.device_status(ws, K, M)
+    want = port.mul_mat(wb, 45, K, x)
+    for f in full:
+        g = f.cpu().numpy()
+        assert_bits(np.ascontiguousarray(g[:, 384:512]), want, "narrow shard, M=%d" % M)
+        assert (g[:, :384] == -1.0).all() and (g[:, 512:] == -1.0).all()
+
