@@ -5,6 +5,8 @@ buffers (torch symmetric memory for the mapping only), every result bit for bit 
     them; M = 1 and 9 take the GEMV, M = 200 the tensor-core kernel (a pair of CTAs).
   * K split: every rank multiplies its slice of x by its block columns, rq_w4a4_sum_partials adds the partials in rank
     order, one shot and two shot; the oracle adds the same partials in the same order.
+  * shared quantizer: every rank rotates and quantizes its own range of tokens, rq_w4a4_share_rows carries the range
+    into the other ranks' workspaces, and every rank then multiplies all tokens.
 
 Skipped with fewer than two devices.  A rank that fails checks its asserts only after its stream is idle, and the waits
 of rq_rank_barrier are bounded, so a failure ends the test instead of hanging it; NVLS is off for NCCL.
@@ -107,6 +109,24 @@ def _rank_main(rank, world, port, results):
             check(y1.view(M, Nk).cpu().numpy(), want, "K split one shot, M=%d" % M)
             check(y2.view(M, Nk).cpu().numpy(), want, "K split two shot, M=%d" % M)
             del keep_p, keep_2
+        # ---- shared quantizer: token ranges quantized apart, exchanged through workspaces mapped into one another
+        K, N, M = 5120, 192, 70
+        wb = port_.quantize_weights(inputs.normal_weights(N, K, 6300), 45)
+        w = rq.Weight(torch.from_numpy(wb).to(dev).view(-1), 45, K, N=N)
+        x = inputs.outlier_activations(M, K, 6301)
+        ws, ws_ptrs, keep_w = mapped(rq.workspace_bytes(K, M), torch.uint8)
+        rq.init_workspace(ws, K, M)
+        lo, hi = rank * M // world, (rank + 1) * M // world
+        fmt = rq.act_format(w, M)
+        meet()                                                          # every workspace is initialised
+        rq.quantize_rows(torch.from_numpy(x[lo:hi]).to(dev), M, lo, w.n_rot, 1.0, 64, fmt, ws)
+        rq.share_rows(ws_ptrs, rank, ws.numel(), K, M, 64, lo, hi - lo)
+        meet()
+        y = rq.mul_mat_quantized(w, M, ws, act_group=64)
+        torch.cuda.synchronize()
+        check(y.cpu().numpy(), port_.mul_mat(wb, 45, K, x), "shared quantizer")
+        meet()
+        del keep_w
         torch.cuda.synchronize()
         if int(status.item()) != 0:
             failures.append("rank %d: a barrier's bounded wait expired (status %d)" % (rank, int(status.item())))
