@@ -32,6 +32,7 @@
 #include <stdlib.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "rq_common.cuh"
 
@@ -555,6 +556,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             int since = 0, n_rec = 0;
             int4 mcur = load_m4(0);
+            const bool fast4 = (n_ag & 3) == 0;        // then the running group count is a multiple of four at every four groups
             // Software pipeline over 32-column pieces of the accumulator: the tensor-memory load of piece c+1 is in flight
             // while piece c folds, and the first piece of the NEXT group is requested (its barrier permitting) before the
             // last piece of this group folds, so a warp never sits out a whole load latency.
@@ -568,45 +570,62 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 const int mq[4] = { mcur.x, mcur.y, mcur.z, mcur.w };
                 if (ag + 4 < n_ag) mcur = load_m4(ag + 4);
                 const int cnt = n_ag - ag < 4 ? n_ag - ag : 4;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (j < cnt && ok) {
-                        const uint32_t buf = gcount & 1u;
-                        const uint32_t t0 = lane_base + buf * BN;
-                        uint64_t mf2 = 0;
-                        if constexpr (F8) mf2 = pack2((uint32_t) mq[j], (uint32_t) mq[j]);      // f32 bits of m / 16, twice
-                        const int mm = mq[j];
-                        RQ_CYC_BEGIN(c_hold);
-                        tmem_ld_wait(va); tmem_ld32(t0 + 32, vb);
-                        if constexpr (F8) fold32_f8<0>(tf, va, mf2); else fold32_i8<0>(tot, va, mm);
-                        tmem_ld_wait(vb); tmem_ld32(t0 + 64, va);
-                        if constexpr (F8) fold32_f8<32>(tf, vb, mf2); else fold32_i8<32>(tot, vb, mm);
-                        tmem_ld_wait(va); tmem_ld32(t0 + 96, vb);
-                        if constexpr (F8) fold32_f8<64>(tf, va, mf2); else fold32_i8<64>(tot, va, mm);
-                        tmem_ld_wait(vb);
-                        // the accumulator is in registers: hand the buffer back before the last piece is folded
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
-                            else      mbar_arrive(empty_bar0 + buf * 8u);
-                        }
-                        RQ_CYC_END(c_hold);
-                        RQ_CYC_BEGIN(c_tail);
-                        ++gcount;
-                        if (ag + j + 1 < n_ag) {
-                            // the loads are warp-collective: leave the loop together or not at all
-                            RQ_CYC_BEGIN(c_tfull);
-                            ok = __all_sync(0xffffffffu, mbar_wait(full_bar0 + (gcount & 1u) * 8u, (gcount >> 1) & 1u, abort_flag));
-                            RQ_CYC_END(c_tfull);
-                            if (ok) {
-                                tc_fence_after();
-                                tmem_ld32(lane_base + (gcount & 1u) * BN, va);
-                            }
-                        }
-                        if constexpr (F8) fold32_f8<96>(tf, vb, mf2); else fold32_i8<96>(tot, vb, mm);
-                        RQ_CYC_END(c_tail);
+                // One group.  FAST: the unit's groups come in fours (always with groups of 64 inputs), so the accumulator
+                // buffer and the barrier phase of group j of the four are known when the code is compiled, up to the
+                // phase p0 the four start with -- the integer instructions that would derive them from the running
+                // count run at half rate and hold the issue port.
+                auto group = [&](auto jc, auto fc, uint32_t p0) {
+                    constexpr int J = decltype(jc)::value;
+                    constexpr bool FAST = decltype(fc)::value;
+                    const uint32_t buf = FAST ? (uint32_t) (J & 1) : (gcount & 1u);
+                    const uint32_t t0 = lane_base + buf * BN;
+                    uint64_t mf2 = 0;
+                    if constexpr (F8) mf2 = pack2((uint32_t) mq[J], (uint32_t) mq[J]);      // f32 bits of m / 16, twice
+                    const int mm = mq[J];
+                    RQ_CYC_BEGIN(c_hold);
+                    tmem_ld_wait(va); tmem_ld32(t0 + 32, vb);
+                    if constexpr (F8) fold32_f8<0>(tf, va, mf2); else fold32_i8<0>(tot, va, mm);
+                    tmem_ld_wait(vb); tmem_ld32(t0 + 64, va);
+                    if constexpr (F8) fold32_f8<32>(tf, vb, mf2); else fold32_i8<32>(tot, vb, mm);
+                    tmem_ld_wait(va); tmem_ld32(t0 + 96, vb);
+                    if constexpr (F8) fold32_f8<64>(tf, va, mf2); else fold32_i8<64>(tot, va, mm);
+                    tmem_ld_wait(vb);
+                    // the accumulator is in registers: hand the buffer back before the last piece is folded
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
+                        else      mbar_arrive(empty_bar0 + buf * 8u);
                     }
+                    RQ_CYC_END(c_hold);
+                    RQ_CYC_BEGIN(c_tail);
+                    ++gcount;
+                    if (FAST ? (J < 3 || ag + 4 < n_ag) : (ag + J + 1 < n_ag)) {
+                        const uint32_t nbuf = FAST ? (uint32_t) ((J + 1) & 1) : (gcount & 1u);
+                        const uint32_t nph = FAST ? (p0 ^ (uint32_t) (((J + 1) >> 1) & 1)) : ((gcount >> 1) & 1u);
+                        // the loads are warp-collective: leave the loop together or not at all
+                        RQ_CYC_BEGIN(c_tfull);
+                        ok = __all_sync(0xffffffffu, mbar_wait(full_bar0 + nbuf * 8u, nph, abort_flag));
+                        RQ_CYC_END(c_tfull);
+                        if (ok) {
+                            tc_fence_after();
+                            tmem_ld32(lane_base + nbuf * BN, va);
+                        }
+                    }
+                    if constexpr (F8) fold32_f8<96>(tf, vb, mf2); else fold32_i8<96>(tot, vb, mm);
+                    RQ_CYC_END(c_tail);
+                };
+                if (fast4) {
+                    const uint32_t p0 = (gcount >> 1) & 1u;
+                    if (ok) group(std::integral_constant<int, 0>{}, std::true_type{}, p0);
+                    if (ok) group(std::integral_constant<int, 1>{}, std::true_type{}, p0);
+                    if (ok) group(std::integral_constant<int, 2>{}, std::true_type{}, p0);
+                    if (ok) group(std::integral_constant<int, 3>{}, std::true_type{}, p0);
+                } else {
+                    if (0 < cnt && ok) group(std::integral_constant<int, 0>{}, std::false_type{}, 0u);
+                    if (1 < cnt && ok) group(std::integral_constant<int, 1>{}, std::false_type{}, 0u);
+                    if (2 < cnt && ok) group(std::integral_constant<int, 2>{}, std::false_type{}, 0u);
+                    if (3 < cnt && ok) group(std::integral_constant<int, 3>{}, std::false_type{}, 0u);
                 }
                 if constexpr (F8) {
                     since += cnt;
