@@ -97,6 +97,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
 }
+// lane 0's arrival as a predicated instruction: no branch, no reconvergence around it
+__device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, int lane) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.s32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" :: "r"(bar), "r"(lane) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_lane0(uint32_t cluster_addr, int lane) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.s32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cluster.b64 _, [%0];\n\t}" :: "r"(cluster_addr), "r"(lane) : "memory");
+}
 __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -593,10 +600,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     // the accumulator is in registers: hand the buffer back before the last piece is folded
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR) mbar_arrive_cluster(empty_bar0 + buf * 8u);
-                        else      mbar_arrive(empty_bar0 + buf * 8u);
-                    }
+                    if (PAIR) mbar_arrive_cluster_lane0(empty_bar0 + buf * 8u, lane);
+                    else      mbar_arrive_lane0(empty_bar0 + buf * 8u, lane);
                     RQ_CYC_END(c_hold);
                     RQ_CYC_BEGIN(c_tail);
                     ++gcount;
@@ -647,7 +652,9 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // but a row-per-thread store would scatter 16-byte pieces over 32 rows: the warp transposes 32 x 32
                 // pieces through shared memory (16-byte chunks XOR-swizzled by row, conflict-free both ways), after which
                 // eight lanes write 128 contiguous bytes of a row and apply s_w, which is per column.
-                const float ut = row_ok ? __ldg(prm.u + row) : 0.0f;
+                // (total * 16) * u as ONE multiply by 16u: the factor 16 is exact on either side (u = R / 3825 with R a
+                // finite float difference cannot overflow times 16), so the product is rounded once, from the same real
+                const float ut16 = __fmul_rn(row_ok ? __ldg(prm.u + row) : 0.0f, 16.0f);
                 const int jj = lane & 7, rsub = lane >> 3;
                 const bool sw_vec = (reinterpret_cast<uintptr_t>(prm.sw) & 15) == 0;
                 auto piece_col = [&](int c) -> int { return n_tile * BN + half * 128 + c * 32 + jj * 4; };
@@ -695,7 +702,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             } else {
                                 totalf = (float) tot[F8 ? 0 : i + k];
                             }
-                            f[k] = __fmul_rn(__fmul_rn(totalf, 16.0f), ut);
+                            f[k] = __fmul_rn(totalf, ut16);
                         }
                         *reinterpret_cast<float4 *>(stg + lane * 32 + ((j ^ (lane & 7)) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
                     }
