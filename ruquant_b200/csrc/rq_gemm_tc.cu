@@ -227,7 +227,8 @@ __device__ __forceinline__ void fold32_f8(uint64_t (&tf)[64], const int (&v)[32]
 // 2.94 M per 1536 inputs, on top of t in [0, 2^20): the float stays inside [2^23 + 2^22 - 2.94 M, 2^23 + 2^22 + 2^20 +
 // 2.94 M), within the window; K <= 32768 has at most 32 re-centrings (groups of 256 re-centre every 1024 inputs, the
 // nearest multiple of four groups), so a byte holds at most 32 * 7 = 224.  At the end
-//     total = (sum of digits - 4 * number of re-centrings) * 2^20 + (mantissa & (2^20 - 1)).
+//     total = (sum of digits - 4 * number of re-centrings) * 2^20 + (float - 1.5 * 2^23),
+// the last term being t, whatever its size: the end of a unit needs no re-centring of its own.
 constexpr int RECENTER_INPUTS = 1536;
 // The carry words live in shared memory between re-centrings (the per-warp tile that later stages the transposed
 // store; word w of lane l at w * 32 + l: conflict-free) -- the registers they would take are the difference between a
@@ -634,7 +635,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
                 if constexpr (F8) {
                     since += cnt;
-                    if (since >= recenter_every || ag + 4 >= n_ag) {
+                    if (since >= recenter_every) {          // (none at the end of the unit: the final conversion takes the total as it stands)
                         RQ_CYC_BEGIN(c_rec);
                         recenter(tf, carry_smem); since = 0; ++n_rec;
                         RQ_CYC_END(c_rec);
@@ -668,7 +669,9 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // float(total) without integer conversions (they run at a quarter of the FMA rate): the digit byte becomes
                 // the mantissa of 2^23 + digit with one byte permute, both parts are made floats by exact subtractions, and
                 // one fused multiply-add forms digit * 2^20 + low with the single round-to-nearest an int -> float
-                // conversion of the total would make.  Every re-centring left the digit at 4.
+                // conversion of the total would make.  Every re-centring moved a digit that stood for digit - 4 units of
+                // 2^20 and left 4 behind; what the float holds beyond 1.5 * 2^23 now is the rest of the total, whatever its
+                // digit reads.
                 const float dsub = 8388608.0f + (float) (4 * n_rec);
                 {
                 // the row units of all four column pieces, requested before anything else: one load latency per unit
