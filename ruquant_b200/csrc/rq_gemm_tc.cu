@@ -672,7 +672,9 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // conversion of the total would make.  Every re-centring moved a digit that stood for digit - 4 units of
                 // 2^20 and left 4 behind; what the float holds beyond 1.5 * 2^23 now is the rest of the total, whatever its
                 // digit reads.
-                const float dsub = 8388608.0f + (float) (4 * n_rec);
+                // (the float itself is 1.5 * 2^23 = 12 * 2^20 plus that rest: the 12 goes into the digit's subtrahend and the
+                // float enters the multiply-add as it is)
+                const float dsub = 8388608.0f + (float) (4 * n_rec + 12);
                 {
                 // the row units of all four column pieces, requested before anything else: one load latency per unit
                 float sc[4][4];
@@ -700,8 +702,7 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                 uint32_t w[2];
                                 unpack2(tf[F8 ? (i + k) >> 1 : 0], w[0], w[1]);
                                 const float df = __fsub_rn(__uint_as_float(prmt(carry[F8 ? i >> 2 : 0], 0x4B000000u, 0x7650u | (uint32_t) k)), dsub);
-                                const float lowf = __fsub_rn(__uint_as_float(w[k & 1]), 12582912.0f);
-                                totalf = __fmaf_rn(df, 1048576.0f, lowf);
+                                totalf = __fmaf_rn(df, 1048576.0f, __uint_as_float(w[k & 1]));
                             } else {
                                 totalf = (float) tot[F8 ? 0 : i + k];
                             }
