@@ -296,7 +296,9 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     __shared__ TcShared sh;
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // (the warp index through a shuffle from lane 0: the compiler then knows that it, and every tensor-memory and barrier
+    // address derived from it, is the same in all lanes, and keeps them in uniform registers)
+    const int warp = __shfl_sync(0xffffffffu, (int) (threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const uint32_t rank = PAIR ? (blockIdx.x & 1u) : 0u;      // rank in the cluster; rank 0 issues the pair's MMAs
     const bool leader = rank == 0;
     const int n_ks = prm.K / BK;          // ring slices of 128 inputs
