@@ -253,10 +253,10 @@ __device__ __forceinline__ void recenter(uint64_t (&tf)[64], uint32_t * carry_sm
         // a reduction without a return value: nothing waits for shared memory here (a load-add-store chain per word
         // would, the fold leaves no registers to batch the loads)
         asm volatile("red.shared.add.u32 [%0], %1;" :: "r"(base + (uint32_t) (i * 128)), "r"(cw) : "memory");
-#pragma unroll
-        for (int h = 0; h < 4; ++h) w[h] = (w[h] & 0xFF8FFFFFu) | 0x00400000u;
-        tf[2 * i] = pack2(w[0], w[1]);
-        tf[2 * i + 1] = pack2(w[2], w[3]);
+        // the digits are reset on the 64-bit pairs where they live: two logic ops per pair on its own halves -- taking the
+        // halves apart, changing them and packing them again cost four register moves per pair on top
+        tf[2 * i] = (tf[2 * i] & 0xFF8FFFFFFF8FFFFFull) | 0x0040000000400000ull;
+        tf[2 * i + 1] = (tf[2 * i + 1] & 0xFF8FFFFFFF8FFFFFull) | 0x0040000000400000ull;
     }
 }
 
