@@ -515,7 +515,10 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
         const int e = warp - 4, quarter = warp & 3, half = e >> 2;
-        const uint32_t lane_base = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (half * 128);
+        uint32_t lane_base = tmem_base + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (half * 128);
+        // (opaque to the compiler from here on: it would otherwise rebuild the address from the warp index -- seven integer
+        // instructions -- in front of every tensor-memory load instead of keeping it in a register)
+        asm volatile("" : "+r"(lane_base));
         // the quantizer records the format it wrote: refuse to multiply the wrong one
         const bool fmt_ok = prm.status == nullptr || prm.status[1] == (F8 ? RQ_FMT_E4M3 : RQ_FMT_I8);
         const uint32_t empty_bar0 = PAIR ? map_to_cta(smem_u32(&sh.tmem_empty[0]), 0) : smem_u32(&sh.tmem_empty[0]);
@@ -624,7 +627,8 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     RQ_CYC_END(c_tail);
                 };
                 if (fast4) {
-                    const uint32_t p0 = (gcount >> 1) & 1u;
+                    uint32_t p0 = (gcount >> 1) & 1u;
+                    asm volatile("" : "+r"(p0));           // (likewise: one value per four groups, not three instructions per use)
                     if (ok) group(std::integral_constant<int, 0>{}, std::true_type{}, p0);
                     if (ok) group(std::integral_constant<int, 1>{}, std::true_type{}, p0);
                     if (ok) group(std::integral_constant<int, 2>{}, std::true_type{}, p0);
