@@ -663,6 +663,14 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // finite float difference cannot overflow times 16), so the product is rounded once, from the same real
                 const float ut16 = __fmul_rn(row_ok ? __ldg(prm.u + row) : 0.0f, 16.0f);
                 const int jj = lane & 7, rsub = lane >> 3;
+                // Shared-memory addresses of the transposition, kept in registers (opaque to the compiler, which would
+                // otherwise rebuild each from the warp and lane indices -- a dozen integer instructions -- at every access):
+                // this lane's row for the stores with its swizzle term, and for the loads row rsub with the term of
+                // (row, 16-byte chunk jj); rows it8*4 + rsub differ from it by 512 bytes per step and, in the swizzle, by
+                // the bit of it8's parity.
+                uint32_t st_addr = smem_u32(stg) + (uint32_t) lane * 128u, st_x = (uint32_t) (lane & 7) << 4;
+                uint32_t ld_addr = smem_u32(stg) + (uint32_t) rsub * 128u, ld_x = (uint32_t) (jj ^ rsub) << 4;
+                asm volatile("" : "+r"(st_addr), "+r"(st_x), "+r"(ld_addr), "+r"(ld_x));
                 const bool sw_vec = (reinterpret_cast<uintptr_t>(prm.sw) & 15) == 0;
                 auto piece_col = [&](int c) -> int { return n_tile * BN + half * 128 + c * 32 + jj * 4; };
                 // the carry words come back into registers (the fold's load buffers are free now) before the tile is reused
@@ -714,19 +722,22 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             }
                             f[k] = __fmul_rn(totalf, ut16);
                         }
-                        *reinterpret_cast<float4 *>(stg + lane * 32 + ((j ^ (lane & 7)) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     :: "r"(st_addr + (st_x ^ (uint32_t) (j << 4))), "f"(f[0]), "f"(f[1]), "f"(f[2]), "f"(f[3]) : "memory");
                     }
                     __syncwarp();
                     const int ncol = piece_col(c);
+                    float * yrow = prm.y + (size_t) (m_tile * BM + quarter * 32 + rsub) * prm.ldy + ncol;      // row rsub; + 4 rows per step
 #pragma unroll
                     for (int it8 = 0; it8 < 8; ++it8) {
-                        const int rr = it8 * 4 + rsub;
-                        const int grow = m_tile * BM + quarter * 32 + rr;
-                        const float4 q = *reinterpret_cast<const float4 *>(stg + rr * 32 + ((jj ^ (rr & 7)) << 2));
+                        const int grow = m_tile * BM + quarter * 32 + it8 * 4 + rsub;
+                        float4 q;       // row it8*4 + rsub, chunk jj ^ (row & 7) = jj ^ rsub ^ 4*(it8 & 1)
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w)
+                                     : "r"(ld_addr + (uint32_t) (it8 * 512) + (ld_x ^ (uint32_t) ((it8 & 1) << 6))) : "memory");
                         const float o0 = __fmul_rn(q.x, sc[c][0]), o1 = __fmul_rn(q.y, sc[c][1]), o2 = __fmul_rn(q.z, sc[c][2]), o3 = __fmul_rn(q.w, sc[c][3]);
                         if (grow < prm.M) {
                             // this GPU's buffer; N-sharded ranks get their copies from warps 2 and 3
-                            float * yr = prm.y + (size_t) grow * prm.ldy + ncol;
+                            float * yr = yrow + (size_t) (it8 * 4) * prm.ldy;
                             if (vec && ncol + 3 < prm.N) {
                                 *reinterpret_cast<float4 *>(yr) = make_float4(o0, o1, o2, o3);
                             } else {
