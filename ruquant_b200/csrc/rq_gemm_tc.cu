@@ -544,11 +544,14 @@ rq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int row = m_tile * BM + quarter * 32 + lane;
             const bool row_ok = row < prm.M;
             const int32_t * mrow = prm.msh + (size_t) (row_ok ? row : 0) * n_ag;
+            int row_live = row_ok ? 1 : 0;
+            // (kept in registers for the unit: rebuilt from the lane index they cost a dozen integer instructions per load)
+            asm volatile("" : "+l"(mrow), "+r"(row_live));
             // the multipliers of four groups at a time (one 16-byte load where a token's row of them is aligned); rows
             // beyond M fold with 0
             auto load_m4 = [&](int ag) -> int4 {
                 int4 r = make_int4(0, 0, 0, 0);
-                if (!row_ok) return r;
+                if (!row_live) return r;
                 if (m_vec) return __ldg(reinterpret_cast<const int4 *>(mrow + ag));
                 r.x = __ldg(mrow + ag);
                 if (ag + 1 < n_ag) r.y = __ldg(mrow + ag + 1);
