@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_cluster_kernel(const ActParams
     const int K = prm.K, m = prm.m, n = prm.n_rot;
     constexpr int NB = P / 4;
     const int nq = m >> 6, units = (K / n) * nq * NB;
+    const int lq = __ffs(nq) - 1;                           // m is a power of two: shifts and masks instead of divisions by nq
     const int nl = (units - rank + C - 1) / C;              // units of this CTA: rank, rank + C, ...
     float * row = smem;
     float * table = row + K;
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_cluster_kernel(const ActParams
     const int col = tid & 63;
     for (int l = tid >> 6; l < nl; l += THREADS / 64) {
         const int v = rank + l * C;
-        const int ab = v % NB, sl = v / NB, js = sl % nq, blk = sl / nq;
+        const int ab = v % NB, sl = v / NB, js = sl & (nq - 1), blk = sl >> lq;
         const float * b = row + (size_t) blk * n + js * 64 + col;
         float colv[P];
 #pragma unroll
@@ -269,7 +270,7 @@ __global__ void __launch_bounds__(THREADS) rq_act_cluster_kernel(const ActParams
         for (int w = tid; w < words; w += nt) {
             const int r = w >> 3, l = r >> 2, k = r & 3;
             const int v = rank + l * C;
-            const int ab = v % NB, sl = v / NB, js = sl % nq, blk = sl / nq;
+            const int ab = v % NB, sl = v / NB, js = sl & (nq - 1), blk = sl >> lq;
             const int kbase = blk * n + (ab * 4 + k) * m + js * 64;         // first input of this group in the row
             const float4 a = reinterpret_cast<float4 *>(outs)[2 * w], b = reinterpret_cast<float4 *>(outs)[2 * w + 1];
             float lo, hi;
