@@ -145,13 +145,14 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? RQ_ACT_MIN_CTAS : 1)
 
     // ---- quantizer: a thread owns a word of 8 values, G/8 neighbouring lanes own a group
     const int lpg = prm.G >> 3, nwords = K >> 3;
+    const int llpg = __ffs(lpg) - 1;                        // G / 8 is a power of two: a shift, not a division, per word
     float tmax = 0.0f;
     for (int w = tid; w < nwords; w += nt) {
         float lo, hi;
         group_range(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1], lpg, prm.clip, lo, hi);
         if ((w & (lpg - 1)) == 0) {
-            g_lo[w / lpg] = lo;
-            g_hi[w / lpg] = hi;
+            g_lo[w >> llpg] = lo;
+            g_hi[w >> llpg] = hi;
         }
         tmax = fmaxf(tmax, __fsub_rn(hi, lo));
     }
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(THREADS, THREADS <= 256 ? RQ_ACT_MIN_CTAS : 1)
     auto store_codes = [&](auto f8) {
         constexpr bool F8 = decltype(f8)::value;
         for (int w = tid; w < nwords; w += nt) {
-            const int g = w / lpg;
+            const int g = w >> llpg;
             float mi;
             const uint2 pk = encode_word<F8>(reinterpret_cast<float4 *>(buf)[2 * w], reinterpret_cast<float4 *>(buf)[2 * w + 1],
                                              g_lo[g], g_hi[g], R, unit, mi);
