@@ -187,7 +187,9 @@ int rq_w4a4_device_status(void * workspace_dev, int64_t K, int64_t M, void * str
 
 /* N-sharded ranks of one node (the reference assembles the outputs with a collective after the node; here the node
  * writes them itself).  rq_w4a4_mul_mat_push is rq_w4a4_mul_mat (GEMV up to 64 tokens: needs the decode layout; tcgen05
- * kernel above: needs the prefill layout) whose epilogue stores every output value into n_dst buffers instead of one: y_dst[d * n_w + i] is weight i's output in destination d
+ * kernel above: needs the prefill layout) that leaves every output value in n_dst buffers instead of one (the GEMV's epilogue
+ * stores it into each; in the tcgen05 kernel two warps copy every finished unit from the first buffer into the others while
+ * the next units are computed): y_dst[d * n_w + i] is weight i's output in destination d
  * -- this rank's own buffer and the peer-mapped buffers of the other ranks (cudaIpc / symmetric memory), all with the
  * same row stride ldy[i].  x_dev may be NULL: the workspace then already holds the quantized activation of all M tokens
  * (rq_w4a4_quantize / rq_w4a4_quantize_rows in the format rq_w4a4_act_format names).  No collective kernel follows.  rq_rank_barrier then makes the pushed data of all ranks
