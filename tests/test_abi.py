@@ -64,6 +64,18 @@ def test_null_arguments_return_status_not_crash(lib):
     assert lib.rq_w4a4_mul_mat(None, 1, None, 0, 1, None, None, 1.0, 64, 0, None, 0, None) == -1
     assert lib.rq_w4a4_quantize(None, 4096, 1, 4096, 0, 1.0, 64, 0, None, 0, None) == -1
     assert lib.rq_w4a4_rotate(None, 4096, 1, 4096, 4096, None, 4096, None) == -1
+    # the multi-rank entry points check their arguments before they touch a device
+    import ctypes
+    two = (ctypes.c_void_p * 2)(None, None)
+    assert lib.rq_w4a4_share_rows(None, 0, 2, 1 << 20, 4096, 8, 64, 0, 4, None) == -1
+    assert lib.rq_w4a4_share_rows(two, 2, 2, 1 << 20, 4096, 8, 64, 0, 4, None) == -1          # rank out of range
+    assert lib.rq_w4a4_share_rows(two, 0, 2, 1 << 20, 4000, 8, 64, 0, 4, None) == -2          # K not a multiple of 256
+    assert lib.rq_w4a4_share_rows(two, 0, 2, 1 << 20, 4096, 8, 64, 6, 4, None) == -2          # rows beyond M_total
+    assert lib.rq_w4a4_share_rows(two, 0, 2, 16, 4096, 8, 64, 0, 4, None) == -5               # workspace too small
+    assert lib.rq_w4a4_share_rows(two, 0, 2, 1 << 20, 4096, 8, 64, 0, 4, None) == -1          # null workspaces
+    assert lib.rq_w4a4_sum_partials(None, 0, 2, 16, None, 0, None) == -1
+    assert lib.rq_w4a4_sum_partials(two, 0, 9, 16, two, 0, None) == -1                        # more ranks than RQ_MAX_RANKS
+    assert lib.rq_rank_barrier(None, 0, 2, None, None, None) == -1
 
 
 ENV_PROBE = r"""
